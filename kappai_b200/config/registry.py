@@ -1,6 +1,7 @@
 """One registry from an architecture's name to its model.
 
-The key is ``config.json``'s ``architectures[0]``.  The reference keeps two
+The key is ``config.json``'s ``architectures[0]``, or its ``architecture`` (one name) where a
+model folder is written that way.  The reference keeps two
 tables (arch flags by GGUF name, src/arch.c:12-114, and constructor-registered
 layer builders, src/recipe.h:577-580, src/recipe/build.c:14-42); here one entry
 carries both: the typed configuration class and the function that turns a
@@ -54,9 +55,13 @@ def architecture_names():
 
 def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
     archs = config_dict.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: missing required key 'architectures' (a list with one name)")
-    return lookup_architecture(archs[0])
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return lookup_architecture(archs[0])
+    one = config_dict.get("architecture")
+    if isinstance(one, str) and one:
+        return lookup_architecture(one)
+    raise ConfigError("config.json: missing required key 'architectures' (a list with one name) "
+                      "or 'architecture' (a name)")
 
 
 def config_from_dict(config_dict: Dict[str, Any]):

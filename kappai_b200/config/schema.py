@@ -131,14 +131,16 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """A block: the arrangement (``block``) of a mixer, a feed-forward and the
-    norms it needs.  Chosen layer by layer."""
+    """A block: the arrangement (``block``, with its constants in
+    ``block_params``) of a mixer, a feed-forward and the norms it needs.  Chosen
+    layer by layer."""
 
     mixer: PartSpec
     ffn: Optional[PartSpec]
     mixer_norm: Optional[PartSpec]
     ffn_norm: Optional[PartSpec]
     block: str = "prenorm_residual"
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
 attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, T* __restrict__ out, int ldo, float scale, int window,
-                      int page_size, int H, int G, int hd) {
+                      int page_size, int H, int G, int hd, int block) {
     kp_pdl_begin();
     __shared__ float qs[KP_MAX_HEAD_DIM];
     __shared__ float ps[ATT_THREADS];
@@ -34,7 +34,8 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
     const int g = h / (H / G);
     const int pos = positions[row];
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
-    const int k_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int k_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (block > 0) k_lo = max(k_lo, (pos / block) * block);      // nothing from before the row's own block of positions
     const int k_hi = pos;
     const size_t page_stride = (size_t)2 * G * page_size * hd;   // elements per page (K and V)
     const size_t k_off = (size_t)g * page_size * hd;
@@ -82,9 +83,11 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
     if (tid + ATT_THREADS < hd) o[tid + ATT_THREADS] = from_f32<T>(acc1 * inv);
 }
 
-extern "C" int kp_attention_rows(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                                 const int* row_seg, const int* positions, void* out, int ldo, float scale,
-                                 int window, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+// block: 0, or the size of the blocks of positions (counted from 0) beyond whose start a row reads no keys.
+extern "C" int kp_attention_rows_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                        const int* row_seg, const int* positions, void* out, int ldo, float scale,
+                                        int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
+                                        void* stream) {
     if (n <= 0) return 0;
     if (hd < 2 || hd > KP_MAX_HEAD_DIM) return KP_ERR_UNSUPPORTED;
     if (G < 1 || H % G != 0 || page_size < 1) return KP_ERR_BAD_ARG;
@@ -92,6 +95,13 @@ extern "C" int kp_attention_rows(const void* q, int ldq, const void* cache, cons
     dim3 grid(H, n);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attention_rows_kernel<T>, dim3(grid), dim3(ATT_THREADS), 0, (cudaStream_t)stream, 
         (const T*)q, ldq, (const T*)cache, block_table, max_blocks, row_seg, positions, (T*)out, ldo, scale, window,
-        page_size, H, G, hd)));
+        page_size, H, G, hd, block)));
     return kp_launch_status();
+}
+
+extern "C" int kp_attention_rows(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                 const int* row_seg, const int* positions, void* out, int ldo, float scale,
+                                 int window, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+    return kp_attention_rows_masked(q, ldq, cache, block_table, max_blocks, row_seg, positions, out, ldo, scale, window, 0,
+                                    page_size, n, H, G, hd, dtype, stream);
 }

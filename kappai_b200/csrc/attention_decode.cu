@@ -37,8 +37,11 @@ __device__ __forceinline__ void unpack16<float>(const uint4& v, float* f) {
     f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
 }
 
-__device__ __forceinline__ void key_range(int pos, int window, int& k_lo, int& k_hi) {
+// The keys a row at position `pos` reads: the last `window` ones (window > 0), and with block > 0 none from
+// before the start of its own block of `block` positions, blocks being counted from position 0 of the sequence.
+__device__ __forceinline__ void key_range(int pos, int window, int block, int& k_lo, int& k_hi) {
     k_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (block > 0) k_lo = max(k_lo, (pos / block) * block);
     k_hi = pos;
 }
 
@@ -49,7 +52,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, const int* __restrict__ block_table,
                   int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
-                  int page_size, int H, int G, int hd_rt) {
+                  int page_size, int H, int G, int hd_rt, int block) {
     kp_pdl_begin();
     extern __shared__ float smem[];
     const int hd = HD ? HD : hd_rt;
@@ -63,7 +66,7 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunk = blockIdx.x, g = blockIdx.y, row = blockIdx.z;
     int k_lo, k_hi;
-    key_range(positions[row], window, k_lo, k_hi);
+    key_range(positions[row], window, block, k_lo, k_hi);
     const int c0 = chunk * AD_CHUNK;
     if (c0 > k_hi || c0 + AD_CHUNK - 1 < k_lo) return;          // the chunk holds none of this row's keys
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
@@ -225,12 +228,12 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
-                                  int chunk_keys, int window, int H, int hd) {
+                                  int chunk_keys, int window, int H, int hd, int block) {
     kp_pdl_begin_early_if(gridDim.y > 1);
     extern __shared__ __align__(16) float merge_sm[];       // [MERGE_BATCH], [n_chunks] l_c, [n_chunks] exp(m_c - m), [32]
     const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
     int k_lo, k_hi;
-    key_range(positions[row], window, k_lo, k_hi);
+    key_range(positions[row], window, block, k_lo, k_hi);
     // (a position beyond the chunks the caller gave is the caller's fault; the clamp keeps the reads inside
     // the scratch and the shared arrays all the same)
     const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi), n = c_hi - c_lo + 1;
@@ -297,14 +300,14 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
 template <typename T>
 __global__ void attn_merge_warp_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
-                                       int chunk_keys, int window, int H, int hd, int n_rows) {
+                                       int chunk_keys, int window, int H, int hd, int n_rows, int block) {
     kp_pdl_begin_early_if(n_rows > 1);
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);          // (row, head)
     if (item >= n_rows * H) return;
     const int row = item / H, h = item - row * H;
     int k_lo, k_hi;
-    key_range(positions[row], window, k_lo, k_hi);
+    key_range(positions[row], window, block, k_lo, k_hi);
     const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi), n = c_hi - c_lo + 1;
     const float* pa = part_acc + (((size_t)row * H + h) * n_chunks + c_lo) * hd;
     const float* ml = part_ml + (((size_t)row * H + h) * n_chunks + c_lo) * 2;
@@ -353,11 +356,11 @@ static size_t merge_smem_bytes(int n_chunks) { return sizeof(float) * ((size_t)2
 
 template <typename T>
 static int launch_merge(const float* part_acc, const float* part_ml, const int* positions, void* out, int ldo,
-                        int n_chunks, int chunk_keys, int window, int n, int H, int hd, cudaStream_t s) {
+                        int n_chunks, int chunk_keys, int window, int block, int n, int H, int hd, cudaStream_t s) {
     if (n_chunks <= MERGE_WARP_CHUNKS && hd <= 128) {
         const int warps = 8;
         kp_launch_pdl(attn_merge_warp_kernel<T>, dim3((n * H + warps - 1) / warps), dim3(warps * 32), 0, s, part_acc, part_ml,
-                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n);
+                      positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd, n, block);
         return kp_launch_status();
     }
     const size_t smem = merge_smem_bytes(n_chunks);
@@ -368,7 +371,7 @@ static int launch_merge(const float* part_acc, const float* part_ml, const int* 
     }
     if (hd > MERGE_THREADS || (hd & 3)) return KP_ERR_UNSUPPORTED;
     kp_launch_pdl(attn_merge_kernel<T>, dim3(H, n), dim3(MERGE_THREADS), smem, s, part_acc, part_ml, positions, (T*)out, ldo,
-                  n_chunks, chunk_keys, window, H, hd);
+                  n_chunks, chunk_keys, window, H, hd, block);
     return kp_launch_status();
 }
 
@@ -386,9 +389,11 @@ long long kp_attention_split_scratch(int n_rows, int H, int hd, int n_chunks) {
 }
 
 // n_chunks: chunks of 256 keys the grid covers; must reach the largest position in the batch.
-int kp_attention_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                       const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
-                       float scale, int window, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+// block: 0, or the size of the blocks of positions that a row's keys do not reach beyond (see key_range).
+int kp_attention_split_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                              const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
+                              float scale, int window, int block, int page_size, int n, int H, int G, int hd, int dtype,
+                              void* stream) {
     if (n <= 0) return 0;
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || (hd & 15)) return KP_ERR_UNSUPPORTED;
     if (G < 1 || H % G != 0 || H / G > AD_RMAX || page_size < 1 || n_chunks < 1) return KP_ERR_UNSUPPORTED;
@@ -402,7 +407,7 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
 #define AD_LAUNCH(T, HD, RR)                                                                                      \
     kp_launch_pdl(attn_split_kernel<T, HD, RR>, dim3(grid), dim3(AD_THREADS), smem, s, (const T*)q, ldq, (const T*)cache, block_table,       \
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
-                                                                n_chunks, scale, window, page_size, H, G, hd)
+                                                                n_chunks, scale, window, page_size, H, G, hd, block)
     KP_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e0;
         if (hd == 64 && R == 4) e0 = AD_LAUNCH(T, 64, 4);
@@ -410,23 +415,35 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
         else if (hd == 128) e0 = AD_LAUNCH(T, 128, 0);
         else e0 = AD_LAUNCH(T, 0, 0);
         if (e0 != cudaSuccess) { cudaGetLastError(); return (int)e0; }      // the first launch that failed
-        return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, AD_CHUNK, window, n, H, hd, s);
+        return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, AD_CHUNK, window, block, n, H, hd, s);
     });
 #undef AD_LAUNCH
     return kp_launch_status();
 }
 
+int kp_attention_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                       const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
+                       float scale, int window, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+    return kp_attention_split_masked(q, ldq, cache, block_table, max_blocks, row_seg, positions, out, ldo, scratch,
+                                     n_chunks, scale, window, 0, page_size, n, H, G, hd, dtype, stream);
+}
+
 // The merge alone, for partials of chunks of `chunk_keys` keys that another kernel wrote into `scratch` in the
 // same format.
-int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int chunk_keys,
-                       int window, int n, int H, int hd, int dtype, void* stream) {
+int kp_attention_merge_masked(const int* positions, void* out, int ldo, const float* scratch, int n_chunks,
+                              int chunk_keys, int window, int block, int n, int H, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535 || chunk_keys < 1) return KP_ERR_UNSUPPORTED;
     const float* part_acc = scratch;
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     KP_DISPATCH_DTYPE(dtype, T, return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, chunk_keys, window,
-                                                       n, H, hd, (cudaStream_t)stream));
+                                                       block, n, H, hd, (cudaStream_t)stream));
     return kp_launch_status();
+}
+
+int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int chunk_keys,
+                       int window, int n, int H, int hd, int dtype, void* stream) {
+    return kp_attention_merge_masked(positions, out, ldo, scratch, n_chunks, chunk_keys, window, 0, n, H, hd, dtype, stream);
 }
 
 }  // extern "C"

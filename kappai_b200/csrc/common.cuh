@@ -29,6 +29,29 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// Activations of the gated feed-forward units, act(gate) * up.  The code travels as an int through the
+// launchers: 0 silu, g / (1 + exp(-g)); 1 relu; 2 gelu in its tanh form,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+#define KP_ACT_SILU 0
+#define KP_ACT_RELU 1
+#define KP_ACT_GELU_TANH 2
+template <int ACT> __device__ __forceinline__ float kp_act(float g) {
+    if (ACT == KP_ACT_RELU) return fmaxf(g, 0.f);
+    if (ACT == KP_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+__device__ __forceinline__ float kp_act_rt(int act, float g) {
+    return act == KP_ACT_RELU ? kp_act<KP_ACT_RELU>(g) : (act == KP_ACT_GELU_TANH ? kp_act<KP_ACT_GELU_TANH>(g) : kp_act<KP_ACT_SILU>(g));
+}
+
+// For the epilogues of the products (a cheap choice at run time: silu unless relu is asked for).  A launcher's
+// `epi` argument carries the activation of its gated epilogue in bits 8 and up.
+__device__ __forceinline__ float kp_act_silu_or_relu(int act, float g) {
+    return act == KP_ACT_RELU ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
+}
+#define KP_EPI_ACT(epi) (((epi) >> 8) & 0xff)
+#define KP_EPI_KIND(epi) ((epi) & 0xff)
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -86,6 +86,7 @@ struct StreamArgs {
     void* C; int ldc;
     int M, N, K, ff;                     // ff: output columns of an epilogue that joins rows of W (SwiGLU: N / 2; conv step: N / 3)
     int n_stages;                        // stages of the ring
+    int act;                             // activation of the gated epilogue (common.cuh)
     // the conv step (EPI_CONV_STEP): taps [ff][conv_k], optional bias [ff], state [slots][conv_k - 1][ff], and for
     // every row its position (0: the state counts as zero) and its state slot
     const float* conv_w; const float* conv_bias; float* conv_state;
@@ -317,7 +318,7 @@ gemm_stream_kernel(const StreamArgs p) {
                 if (p.bias) u += p.bias[p.ff + n];
                 // gate and up are rounded to the storage type before the activation, as the unfused path stores them
                 const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-                ((bf16*)p.C)[o] = from_f32<bf16>((gq / (1.0f + expf(-gq))) * uq);
+                ((bf16*)p.C)[o] = from_f32<bf16>(kp_act_silu_or_relu(p.act, gq) * uq);
             } else if (EPI == EPI_STORE) {
                 ((bf16*)p.C)[o] = from_f32<bf16>(v);
             } else if (EPI == EPI_STORE_F32) {
@@ -422,6 +423,9 @@ int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* 
                    int K, int epi, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     StreamArgs a = {};
+    a.act = KP_EPI_ACT(epi);
+    epi = KP_EPI_KIND(epi);
+    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU) return KP_ERR_UNSUPPORTED;
     int st = check_common(a, M, N, K, ldw, W, epi);
     if (st) return st;
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;

@@ -54,6 +54,7 @@ struct TcArgs {
     const float* bias;
     void* C; int ldc;
     int M, N, K, ff;
+    int act;                                // activation of the gated epilogue (common.cuh)
     int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
     int a_rows;                             // rows of the A box: 128, fewer (a multiple of 8) when M < 128
     int n_stages;                           // stages of the ring
@@ -98,7 +99,7 @@ __device__ __forceinline__ void tc_finish(const TcArgs& p, int n_lim, const floa
             if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
             // gate and up are rounded to the storage type first, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-            x = (gq / (1.0f + expf(-gq))) * uq;
+            x = kp_act_silu_or_relu(p.act, gq) * uq;
         }
         v[j] = x;
     }
@@ -523,10 +524,13 @@ extern "C" {
 int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                      int K, int epi, int split, void* stream) {
     if (M <= 0 || N <= 0) return 0;
+    const int act = KP_EPI_ACT(epi);
+    epi = KP_EPI_KIND(epi);
+    if (act != KP_ACT_SILU && act != KP_ACT_RELU) return KP_ERR_UNSUPPORTED;
     if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
     TcArgs a = {};
-    a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.ff = 0;
+    a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.ff = 0; a.act = act;
     {
         const int esz = (epi == EPI_STORE || epi == EPI_SWIGLU) ? 2 : 4;
         a.vec_ok = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * esz) % 16 == 0) ? 1 : 0;

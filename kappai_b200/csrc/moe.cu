@@ -1,0 +1,436 @@
+// Mixture of experts: every row (token) runs `top` of E small gated feed-forward units and adds their
+// outputs, weighted, to the float32 residual.
+//
+//   z = router logits [n, E] (float32, computed by the caller)
+//   chosen(r) = the `top` largest z[r, :] (ties: the lower index), weights = softmax over the chosen logits only
+//   out[r, :] += sum_j weight_j * Wd_e (act(Wg_e h_r) * (Wu_e h_r)),  e = chosen_j(r), j in order
+//
+// Which rows meet which expert is known on the device only, so the work is laid out there too and nothing
+// comes back to the host (a step with this layer can be captured in a CUDA graph):
+//   moe_route:  one warp a row picks the experts and their weights;
+//   moe_sort:   one CTA counts the (row, choice) pairs of every expert, lays the pairs out expert by expert
+//               (`perm`: place -> pair, `inv`: pair -> place) and lists the row tiles of every expert;
+//   moe_gate_up / moe_down: grouped products over those tiles, a tile being rows of ONE expert, so that its
+//               weights are read once for all of them; every output element sums k in order, whatever the
+//               tile it fell into, so a row's result does not depend on the rest of the batch;
+//   moe_combine: out[r] += sum over j of weight_j * y[place of (r, j)], j ascending.
+// The products exist in two forms: CUDA-core float32 FMA (the true 32-bit path, and every shape), and
+// bfloat16 tensor-core tiles (mma.sync m16n8k16, float32 accumulation) for 16-bit storage.
+#include "common.cuh"
+
+#define MOE_BM 32                // rows of a tile
+#define MOE_MAX_TOP 32
+#define MOE_SORT_THREADS 1024
+
+// ------------------------------------------------------------------------------------------------ route
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* __restrict__ idx_out,
+                 float* __restrict__ w_out) {
+    kp_pdl_begin();
+    extern __shared__ float route_sm[];                         // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= n) return;
+    float* z = route_sm + (size_t)warp * E;
+    for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)r * E + e];
+    __syncwarp();
+    float my_z = -INFINITY;
+    int my_e = 0;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; bi = e; }                 // (ascending e: the first of equal values stays)
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;                           // (a row of NaN or -inf: keep the indices legal)
+        if (lane == j) { my_z = best; my_e = bi; }
+        if (lane == 0) z[bi] = -INFINITY;
+        __syncwarp();
+    }
+    const float m = __shfl_sync(0xffffffffu, my_z, 0);
+    const float p = lane < top ? expf(my_z - m) : 0.f;
+    const float sum = warp_sum(p);
+    if (lane < top) {
+        idx_out[(size_t)r * top + lane] = my_e;
+        w_out[(size_t)r * top + lane] = p / sum;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- sort
+// offsets[e] .. offsets[e+1]: the places of expert e's pairs; tile_start[e] .. tile_start[e+1]: its row tiles
+// of MOE_BM places (tile_start[E] = all tiles).  perm[place] = pair (row * top + j); inv[pair] = place.
+__global__ void __launch_bounds__(MOE_SORT_THREADS)
+moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ offsets, int* __restrict__ tile_start,
+                int* __restrict__ perm, int* __restrict__ inv) {
+    kp_pdl_begin();
+    extern __shared__ int sort_sm[];                            // [E] counts, [E] cursors, [E + 1] offsets
+    int* cnt = sort_sm;
+    int* cur = cnt + E;
+    int* off = cur + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, t = 0;
+        for (int e = 0; e < E; e++) {
+            off[e] = o; offsets[e] = o; tile_start[e] = t;
+            o += cnt[e];
+            t += (cnt[e] + MOE_BM - 1) / MOE_BM;
+        }
+        off[E] = o; offsets[E] = o; tile_start[E] = t;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = idx[p];
+        const int place = off[e] + atomicAdd(&cur[e], 1);
+        perm[place] = p;
+        inv[p] = place;
+    }
+}
+
+// The expert and the rows of row tile `bt` (false: no such tile in this step).
+__device__ __forceinline__ bool moe_tile(const int* __restrict__ offsets, const int* __restrict__ tile_start, int E, int bt,
+                                         int& e, int& row0, int& row1) {
+    if (bt >= tile_start[E]) return false;
+    int lo = 0, hi = E;                                         // the last e with tile_start[e] <= bt
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_start[mid] <= bt) lo = mid; else hi = mid;
+    }
+    e = lo;
+    row0 = offsets[e] + (bt - tile_start[e]) * MOE_BM;
+    row1 = min(row0 + MOE_BM, offsets[e + 1]);
+    return true;
+}
+
+// ---------------------------------------------------------------------------- products on the CUDA cores
+// act[place, c] = f(h_row . Wg_e[c]) * (h_row . Wu_e[c]); gate and up are rounded to the storage type before f,
+// as the dense gated unit does.  w_gu: [E][2 ff][d], gate rows then up rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ w_gu, const int* __restrict__ offsets,
+                   const int* __restrict__ tile_start, const int* __restrict__ perm, T* __restrict__ act, int E, int top,
+                   int d, int ff, int act_kind) {
+    kp_pdl_begin();
+    constexpr int BN = 32, BK = 16;
+    __shared__ float As[BK][MOE_BM + 1], Gs[BK][BN + 1], Us[BK][BN + 1];
+    __shared__ int src_row[MOE_BM];
+    int e, row0, row1;
+    if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const int n0 = blockIdx.x * BN;
+    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? perm[row0 + tid] / top : -1;
+    __syncthreads();
+    const T* wg = w_gu + (size_t)e * 2 * ff * d;
+    const T* wu = wg + (size_t)ff * d;
+    float ag[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, au[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    for (int k0 = 0; k0 < d; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int el = tid + i * 256, r = el / BK, c = el % BK, gk = k0 + c;
+            const int sr = src_row[r];
+            As[c][r] = (sr >= 0 && gk < d) ? to_f32(h[(size_t)sr * ldh + gk]) : 0.f;
+            const bool ok = n0 + r < ff && gk < d;
+            Gs[c][r] = ok ? to_f32(wg[(size_t)(n0 + r) * d + gk]) : 0.f;
+            Us[c][r] = ok ? to_f32(wu[(size_t)(n0 + r) * d + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+            const float g0 = Gs[k][tx * 2], g1 = Gs[k][tx * 2 + 1], u0 = Us[k][tx * 2], u1 = Us[k][tx * 2 + 1];
+            ag[0][0] = fmaf(a0, g0, ag[0][0]); ag[0][1] = fmaf(a0, g1, ag[0][1]);
+            ag[1][0] = fmaf(a1, g0, ag[1][0]); ag[1][1] = fmaf(a1, g1, ag[1][1]);
+            au[0][0] = fmaf(a0, u0, au[0][0]); au[0][1] = fmaf(a0, u1, au[0][1]);
+            au[1][0] = fmaf(a1, u0, au[1][0]); au[1][1] = fmaf(a1, u1, au[1][1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int place = row0 + ty * 2 + i;
+        if (place >= row1) continue;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int c = n0 + tx * 2 + j;
+            if (c >= ff) continue;
+            const float g = to_f32(from_f32<T>(ag[i][j])), u = to_f32(from_f32<T>(au[i][j]));
+            act[(size_t)place * ff + c] = from_f32<T>(kp_act_rt(act_kind, g) * u);
+        }
+    }
+}
+
+// y[place, c] = act[place, :] . Wd_e[c, :]   (float32 out).  w_down: [E][d][ff].
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ offsets,
+                const int* __restrict__ tile_start, float* __restrict__ y, int E, int d, int ff) {
+    kp_pdl_begin();
+    constexpr int BN = 64, BK = 16;
+    __shared__ float As[BK][MOE_BM + 1], Ws[BK][BN + 1];
+    int e, row0, row1;
+    if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
+    const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+    const int n0 = blockIdx.x * BN;
+    const T* wd = w_down + (size_t)e * d * ff;
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < ff; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int el = tid + i * 256, r = el / BK, c = el % BK, gk = k0 + c;
+            As[c][r] = (row0 + r < row1 && gk < ff) ? to_f32(act[(size_t)(row0 + r) * ff + gk]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int el = tid + i * 256, r = el / BK, c = el % BK, gk = k0 + c;
+            Ws[c][r] = (n0 + r < d && gk < ff) ? to_f32(wd[(size_t)(n0 + r) * ff + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float w = Ws[k][tx * 4 + j];
+                acc[0][j] = fmaf(a0, w, acc[0][j]);
+                acc[1][j] = fmaf(a1, w, acc[1][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int place = row0 + ty * 2 + i;
+        if (place >= row1) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = n0 + tx * 4 + j;
+            if (c < d) y[(size_t)place * d + c] = acc[i][j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------ products on the tensor cores
+// The same two products for bfloat16 with mma.sync m16n8k16 (float32 accumulation): a CTA of four warps
+// takes one row tile of 32 places and 64 output columns; warp w owns columns 16 w .. 16 w + 15 (two n-tiles)
+// of both 16-row halves.  Operands go through shared memory in k-blocks of 32 (rows padded to 40 halves: the
+// fragment loads of a warp then fall into different banks).  Needs K % 8 == 0 (16-byte loads).
+#define MOE_TC_BN 64
+#define MOE_TC_BK 32
+#define MOE_TC_LD 40
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// One k-block of NB operand matrices of `rows` rows each into shared memory (16 bytes a thread and turn);
+// rows beyond `valid` (or with a negative source row) and columns beyond K are zero.
+__device__ __forceinline__ void moe_tc_stage(bf16 (*dst)[MOE_TC_LD], int rows, const bf16* src, const int* src_rows,
+                                             long long ld, int first_row, int valid, int k0, int K) {
+    for (int el = threadIdx.x; el < rows * (MOE_TC_BK / 8); el += blockDim.x) {
+        const int r = el / (MOE_TC_BK / 8), c8 = (el % (MOE_TC_BK / 8)) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        long long sr = src_rows ? (long long)src_rows[r] : (r < valid ? (long long)first_row + r : -1);
+        if (sr >= 0 && k0 + c8 < K) v = *reinterpret_cast<const uint4*>(src + sr * ld + k0 + c8);
+        *reinterpret_cast<uint4*>(&dst[r][c8]) = v;
+    }
+}
+
+// acc[half][nt][4] += A[32 x BK] * W[warp's 16 columns x BK]^T for one staged k-block
+__device__ __forceinline__ void moe_tc_block(float (*acc)[2][4], const bf16 (*As)[MOE_TC_LD], const bf16 (*Ws)[MOE_TC_LD],
+                                             int warp, int lane) {
+    const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < MOE_TC_BK; kk += 16) {
+        uint32_t b[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            const bf16* wr = &Ws[warp * 16 + nt * 8 + gid][kk + tig * 2];
+            b[nt][0] = *reinterpret_cast<const uint32_t*>(wr);
+            b[nt][1] = *reinterpret_cast<const uint32_t*>(wr + 8);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            uint32_t a[4];
+            const bf16* ar0 = &As[half * 16 + gid][kk + tig * 2];
+            const bf16* ar1 = &As[half * 16 + gid + 8][kk + tig * 2];
+            a[0] = *reinterpret_cast<const uint32_t*>(ar0);
+            a[1] = *reinterpret_cast<const uint32_t*>(ar1);
+            a[2] = *reinterpret_cast<const uint32_t*>(ar0 + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(ar1 + 8);
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++) mma_bf16_16816(acc[half][nt], a, b[nt]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+moe_gate_up_tc_kernel(const bf16* __restrict__ h, int ldh, const bf16* __restrict__ w_gu, const int* __restrict__ offsets,
+                      const int* __restrict__ tile_start, const int* __restrict__ perm, bf16* __restrict__ act, int E,
+                      int top, int d, int ff, int act_kind) {
+    kp_pdl_begin();
+    __shared__ __align__(16) bf16 As[MOE_BM][MOE_TC_LD], Gs[MOE_TC_BN][MOE_TC_LD], Us[MOE_TC_BN][MOE_TC_LD];
+    __shared__ int src_row[MOE_BM];
+    int e, row0, row1;
+    if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MOE_TC_BN;
+    if (tid < MOE_BM) src_row[tid] = row0 + tid < row1 ? perm[row0 + tid] / top : -1;
+    __syncthreads();
+    const bf16* wg = w_gu + (size_t)e * 2 * ff * d;
+    const bf16* wu = wg + (size_t)ff * d;
+    const int w_valid = min(MOE_TC_BN, ff - n0);
+    float ag[2][2][4] = {}, au[2][2][4] = {};
+    for (int k0 = 0; k0 < d; k0 += MOE_TC_BK) {
+        moe_tc_stage(As, MOE_BM, h, src_row, ldh, 0, 0, k0, d);
+        moe_tc_stage(Gs, MOE_TC_BN, wg, nullptr, d, n0, w_valid, k0, d);
+        moe_tc_stage(Us, MOE_TC_BN, wu, nullptr, d, n0, w_valid, k0, d);
+        __syncthreads();
+        moe_tc_block(ag, As, Gs, warp, lane);
+        moe_tc_block(au, As, Us, warp, lane);
+        __syncthreads();
+    }
+    const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; half++)
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int place = row0 + half * 16 + gid + (i >> 1) * 8;
+                const int c = n0 + warp * 16 + nt * 8 + tig * 2 + (i & 1);
+                if (place < row1 && c < ff) {
+                    const float g = to_f32(__float2bfloat16_rn(ag[half][nt][i])), u = to_f32(__float2bfloat16_rn(au[half][nt][i]));
+                    act[(size_t)place * ff + c] = __float2bfloat16_rn(kp_act_rt(act_kind, g) * u);
+                }
+            }
+}
+
+__global__ void __launch_bounds__(128)
+moe_down_tc_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w_down, const int* __restrict__ offsets,
+                   const int* __restrict__ tile_start, float* __restrict__ y, int E, int d, int ff) {
+    kp_pdl_begin();
+    __shared__ __align__(16) bf16 As[MOE_BM][MOE_TC_LD], Ws[MOE_TC_BN][MOE_TC_LD];
+    int e, row0, row1;
+    if (!moe_tile(offsets, tile_start, E, blockIdx.y, e, row0, row1)) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MOE_TC_BN;
+    const bf16* wd = w_down + (size_t)e * d * ff;
+    const int w_valid = min(MOE_TC_BN, d - n0);
+    float acc[2][2][4] = {};
+    for (int k0 = 0; k0 < ff; k0 += MOE_TC_BK) {
+        moe_tc_stage(As, MOE_BM, act, nullptr, ff, row0, row1 - row0, k0, ff);
+        moe_tc_stage(Ws, MOE_TC_BN, wd, nullptr, ff, n0, w_valid, k0, ff);
+        __syncthreads();
+        moe_tc_block(acc, As, Ws, warp, lane);
+        __syncthreads();
+    }
+    const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+    for (int half = 0; half < 2; half++)
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int place = row0 + half * 16 + gid + (i >> 1) * 8;
+                const int c = n0 + warp * 16 + nt * 8 + tig * 2 + (i & 1);
+                if (place < row1 && c < d) y[(size_t)place * d + c] = acc[half][nt][i];
+            }
+}
+
+// ---------------------------------------------------------------------------------------------- combine
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ w,
+                                   float* __restrict__ out, int n, int d, int top) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / d, c = i % d;
+        float s = 0.f;
+        for (int j = 0; j < top; j++) s = fmaf(w[r * top + j], y[(size_t)inv[r * top + j] * d + c], s);
+        out[i] += s;
+    }
+}
+
+extern "C" {
+
+// Ints of scratch for the layout of one step: offsets [E + 1], tile_start [E + 1], perm [n top], inv [n top].
+long long kp_moe_layout_ints(int n, int E, int top) { return 2LL * (E + 1) + 2LL * n * top; }
+
+// Row tiles a step of n rows can have at most (a grid axis of the grouped products).
+int kp_moe_max_tiles(int n, int E, int top) {
+    const long long pairs = (long long)n * top;
+    return (int)(pairs / MOE_BM + (pairs < E ? pairs : E));
+}
+
+// logits [n, E] float32 -> idx [n, top], weights [n, top], and the layout (see kp_moe_layout_ints).
+int kp_moe_route(const float* logits, int n, int E, int top, int* idx, float* weights, int* layout, void* stream) {
+    if (n <= 0) return 0;
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return KP_ERR_UNSUPPORTED;
+    const size_t route_sm = (size_t)8 * E * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
+    if (route_sm > 48 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;            // (E <= 1536)
+    cudaStream_t s = (cudaStream_t)stream;
+    kp_launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), route_sm, s, logits, n, E, top, idx, weights);
+    cudaError_t e0 = cudaGetLastError();
+    if (e0 != cudaSuccess) return (int)e0;
+    int* offsets = layout;
+    int* tile_start = offsets + (E + 1);
+    int* perm = tile_start + (E + 1);
+    int* inv = perm + (size_t)n * top;
+    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, offsets, tile_start,
+                  perm, inv);
+    return kp_launch_status();
+}
+
+// h [n, d] -> act [n top, ff] (by place) -> y [n top, d] float32 (by place) -> out [n, d] += weighted sum.
+int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
+                   void* act, float* y, float* out, int n, int E, int top, int d, int ff, int act_kind, int dtype,
+                   void* stream) {
+    if (n <= 0) return 0;
+    if (E < 1 || top < 1 || d < 1 || ff < 1 || act_kind < 0 || act_kind > KP_ACT_GELU_TANH) return KP_ERR_BAD_ARG;
+    const int max_tiles = kp_moe_max_tiles(n, E, top);
+    if (max_tiles > 65535) return KP_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int* offsets = layout;
+    const int* tile_start = offsets + (E + 1);
+    const int* perm = tile_start + (E + 1);
+    const int* inv = perm + (size_t)n * top;
+    cudaError_t e0;
+    const bool tc = dtype == KP_DTYPE_BF16 && d % 8 == 0 && ff % 8 == 0 && ldh % 8 == 0 &&
+                    !(((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) & 15);
+    if (tc) {
+        kp_launch_pdl(moe_gate_up_tc_kernel, dim3((ff + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)h,
+                      ldh, (const bf16*)w_gu, offsets, tile_start, perm, (bf16*)act, E, top, d, ff, act_kind);
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        kp_launch_pdl(moe_down_tc_kernel, dim3((d + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)act,
+                      (const bf16*)w_down, offsets, tile_start, y, E, d, ff);
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+    } else {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_gate_up_kernel<T>, dim3((ff + 31) / 32, max_tiles), dim3(256), 0, s,
+                                                   (const T*)h, ldh, (const T*)w_gu, offsets, tile_start, perm, (T*)act, E, top,
+                                                   d, ff, act_kind)));
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_down_kernel<T>, dim3((d + 63) / 64, max_tiles), dim3(256), 0, s,
+                                                   (const T*)act, (const T*)w_down, offsets, tile_start, y, E, d, ff)));
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+    }
+    size_t g = ((size_t)n * d + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    kp_launch_pdl(moe_combine_kernel, dim3((unsigned)g), dim3(256), 0, s, (const float*)y, inv, weights, out, n, d, top);
+    return kp_launch_status();
+}
+
+}  // extern "C"

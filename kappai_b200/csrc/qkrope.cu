@@ -24,7 +24,7 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
                        const float* __restrict__ sin_tab, int rot, int interleaved,
                        const int* __restrict__ positions, const int* __restrict__ slot_map,
                        T* q_out, int ldq, T* __restrict__ cache, int page_size,
-                       int H, int G, int hd, int write_kv) {
+                       int H, int G, int hd, int write_kv, int v_col) {
     kp_pdl_begin();
     __shared__ float buf[4][KP_MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -34,7 +34,9 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
     const int kind = head < H ? 0 : (head < H + G ? 1 : 2);
     const bool in_place = q_out == nullptr;            // norm/rotate q and k where they are; no cache write
     if (kind != 0 && !write_kv && !(in_place && kind == 1)) return;
-    const T* src = qkv + (size_t)row * ld + (size_t)head * hd;
+    // (the values start at column v_col of the row: behind the keys, or at the keys themselves for a design
+    // whose values are its key projections, taken here before the key's norm and rotation)
+    const T* src = qkv + (size_t)row * ld + (kind == 2 ? (size_t)v_col + (size_t)(head - H - G) * hd : (size_t)head * hd);
     float* x = buf[warp];
 
     float ss = 0.f;
@@ -88,7 +90,7 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
                            const float* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                            const float* __restrict__ sin_tab, const int* __restrict__ positions,
                            const int* __restrict__ slot_map, bf16* __restrict__ q_out, int ldq,
-                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv) {
+                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv, int v_col) {
     kp_pdl_begin_early();
     constexpr int L = HD / 8;                          // lanes a head
     constexpr int HPB = 128 / L;                       // heads a block
@@ -98,7 +100,8 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
     const bool live = head < H + 2 * G;
     const int hh = live ? head : 0;
     const int kind = hh < H ? 0 : (hh < H + G ? 1 : 2);
-    const uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + (size_t)hh * HD + lane_in * 8);
+    const size_t col = kind == 2 ? (size_t)v_col + (size_t)(hh - H - G) * HD : (size_t)hh * HD;
+    const uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + col + lane_in * 8);
     float x[8];
     {
         const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -155,29 +158,31 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
 extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, const float* k_w, float eps,
                                   const float* cos_tab, const float* sin_tab, int rot, int interleaved,
                                   const int* positions, const int* slot_map, void* q_out, int ldq, void* cache,
-                                  int page_size, int n, int H, int G, int hd, int write_kv, int dtype, void* stream) {
+                                  int page_size, int n, int H, int G, int hd, int write_kv, int v_col, int dtype,
+                                  void* stream) {
     if (n <= 0) return 0;
+    if (v_col < 0) v_col = (H + G) * hd;
     if (hd < 2 || hd > KP_MAX_HEAD_DIM || (hd & 1)) return KP_ERR_UNSUPPORTED;
     if (cos_tab && (rot < 2 || rot > hd || (rot & 1))) return KP_ERR_BAD_ARG;
     if (n > 65535) return KP_ERR_UNSUPPORTED;
     // the 16-byte form: bfloat16, head size 64 or 128, whole-head NeoX rotation or none, aligned rows
     if (dtype == KP_DTYPE_BF16 && (hd == 64 || hd == 128) && q_out != nullptr && (!cos_tab || (rot == hd && !interleaved)) &&
-        (ld % 8 == 0) && (ldq % 8 == 0) && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15) &&
+        (ld % 8 == 0) && (ldq % 8 == 0) && (v_col % 8 == 0) && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15) &&
         (!q_w || !((uintptr_t)q_w & 15)) && (!k_w || !((uintptr_t)k_w & 15)) &&
         (!cos_tab || (!((uintptr_t)cos_tab & 15) && !((uintptr_t)sin_tab & 15)))) {
         const int hpb = 128 / (hd / 8);
         dim3 vgrid((H + 2 * G + hpb - 1) / hpb, n);
         if (hd == 64)
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<64>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col);
         else
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<128>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col);
         return kp_launch_status();
     }
     dim3 grid((H + 2 * G + 3) / 4, n);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)qkv, ld, q_w, k_w, eps, cos_tab, sin_tab, rot, interleaved, positions, slot_map, (T*)q_out, ldq,
-        (T*)cache, page_size, H, G, hd, write_kv)));
+        (T*)cache, page_size, H, G, hd, write_kv, v_col)));
     return kp_launch_status();
 }

@@ -165,17 +165,72 @@ rmsnorm_rows_blk_kernel(const float* __restrict__ x, const float* __restrict__ w
     if (ib < n4) store4(dst + 4 * ib, (b.x * scale) * wb.x, (b.y * scale) * wb.y, (b.z * scale) * wb.z, (b.w * scale) * wb.w);
 }
 
-// act = silu(gate) * up,  silu(g) = g / (1 + exp(-g))     (src/backend/cpu/scalar/core.c:774-800)
-// gate_up rows hold [gate(ff) | up(ff)].
+// Post-norm step of a residual layer: y = (a * rsqrt(mean(a^2) + eps)) * w for the rows a of `acc` (the
+// float32 sum alpha * x + sublayer(x) of a layer that norms AFTER the sum).  Up to three images of y leave in
+// one pass, each only if its pointer is given: y itself in float32 (`x_out`, the new residual), y in the
+// storage type (`h_out`, what the next sublayer's products read) and alpha * y in float32 (`scaled_out`, the
+// sum the next sublayer adds into).  Every output may be `acc` itself: an element is read and written by the
+// same thread, after the row's statistic is known.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int n, int ff) {
+__global__ void __launch_bounds__(256)
+postnorm_rows_kernel(const float* acc, const float* __restrict__ w, float* x_out, T* h_out, float* scaled_out,
+                     int d, float eps, float alpha) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* src = acc + (size_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float y = (src[i] * scale) * w[i];
+        if (x_out) x_out[(size_t)r * d + i] = y;
+        if (h_out) h_out[(size_t)r * d + i] = from_f32<T>(y);
+        if (scaled_out) scaled_out[(size_t)r * d + i] = alpha * y;
+    }
+}
+
+// The entry of such a layer when nothing has prepared it: h = x in the storage type, scaled = alpha * x.
+template <typename T>
+__global__ void scale_cast_kernel(const float* __restrict__ x, T* __restrict__ h_out, float* __restrict__ scaled_out,
+                                  size_t n, float alpha) {
+    kp_pdl_begin();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        if (h_out) h_out[i] = from_f32<T>(v);
+        scaled_out[i] = alpha * v;
+    }
+}
+
+// o[r, c] *= sigmoid(g[r, c]): an output gate on the concatenated heads, the gate being columns of a wider
+// row (the product that also made q and k).  The sigmoid is float32.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ o, int ldo, const T* __restrict__ g, int ldg, int n, int cols) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols, c = i % cols;
+        const float z = to_f32(g[r * ldg + c]);
+        T* p = o + r * ldo + c;
+        *p = from_f32<T>(to_f32(*p) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+// act = f(gate) * up with f = silu, g / (1 + exp(-g))     (src/backend/cpu/scalar/core.c:774-800),
+// relu or tanh-gelu (`act_kind`, see common.cuh).  gate_up rows hold [gate(ff) | up(ff)].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int n, int ff, int act_kind) {
     kp_pdl_begin();
     const size_t total = (size_t)n * ff;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / ff, c = i % ff;
         const float g = to_f32(gu[r * 2 * ff + c]);
         const float u = to_f32(gu[r * 2 * ff + ff + c]);
-        act[i] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+        act[i] = from_f32<T>(kp_act_rt(act_kind, g) * u);
     }
 }
 
@@ -258,10 +313,37 @@ int kp_rmsnorm_rows(const float* x, const float* w, void* y, const int* rows, in
     return kp_launch_status();
 }
 
-int kp_swiglu(const void* gate_up, void* act, int n, int ff, int dtype, void* stream) {
+int kp_swiglu(const void* gate_up, void* act, int n, int ff, int act_kind, int dtype, void* stream) {
     if (n <= 0) return 0;
+    if (act_kind < 0 || act_kind > KP_ACT_GELU_TANH) return KP_ERR_BAD_ARG;
     const int g = grid_for((size_t)n * ff, 256);
-    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(swiglu_kernel<T>, dim3(g), dim3(256), 0, (cudaStream_t)stream, (const T*)gate_up, (T*)act, n, ff)));
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(swiglu_kernel<T>, dim3(g), dim3(256), 0, (cudaStream_t)stream, (const T*)gate_up, (T*)act, n, ff, act_kind)));
+    return kp_launch_status();
+}
+
+// dtype: the type of h_out.  Any of x_out, h_out, scaled_out may be null.
+int kp_postnorm_rows(const float* acc, const float* w, float* x_out, void* h_out, float* scaled_out, int n, int d,
+                     float eps, float alpha, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(postnorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, acc, w, x_out,
+                                               (T*)h_out, scaled_out, d, eps, alpha)));
+    return kp_launch_status();
+}
+
+int kp_scale_cast(const float* x, void* h_out, float* scaled_out, long long n, float alpha, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    const int g = grid_for((size_t)n, 256);
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(scale_cast_kernel<T>, dim3(g), dim3(256), 0, (cudaStream_t)stream, x, (T*)h_out,
+                                               scaled_out, (size_t)n, alpha)));
+    return kp_launch_status();
+}
+
+int kp_sigmoid_gate(void* o, int ldo, const void* g, int ldg, int n, int cols, int dtype, void* stream) {
+    if (n <= 0 || cols <= 0) return 0;
+    const int gr = grid_for((size_t)n * cols, 256);
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(sigmoid_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo,
+                                               (const T*)g, ldg, n, cols)));
     return kp_launch_status();
 }
 

@@ -31,7 +31,7 @@ class Model:
             ffn = self._make("feed_forward", ls.ffn) if ls.ffn is not None else None
             n1 = self._make("norm", ls.mixer_norm) if ls.mixer_norm is not None else None
             n2 = self._make("norm", ls.ffn_norm) if ls.ffn_norm is not None else None
-            block = make_part("block", PartSpec(ls.block), env)
+            block = make_part("block", PartSpec(ls.block, dict(ls.block_params)), env)
             self.blocks.append(block.assemble(mixer, ffn, n1, n2))
         self.final_norm = self._make("norm", spec.final_norm) if spec.final_norm is not None else None
         self.head = self._make("head", spec.head)

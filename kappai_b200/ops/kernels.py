@@ -292,14 +292,70 @@ def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}     # codes of the gated units' activations (csrc/common.cuh)
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation '{name}': expected one of {', '.join(ACTIVATIONS)}") from None
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """out = act(gate) * up for rows [gate | up]."""
     _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
     n, ff = out.shape
     if gate_up.shape != (n, 2 * ff):
         raise KernelError("swiglu: shape mismatch")
     lib = load_library("rowwise")
-    _run("swiglu", lib.kp_swiglu, _ptr(gate_up), _ptr(out), n, ff, dtype_code(out.dtype), STREAM)
+    _run("swiglu", lib.kp_swiglu, _ptr(gate_up), _ptr(out), n, ff, activation_code(activation), dtype_code(out.dtype), STREAM)
     return out
+
+
+def postnorm_rows(acc: torch.Tensor, w: torch.Tensor, eps: float, x_out: Optional[torch.Tensor] = None,
+                  h_out: Optional[torch.Tensor] = None, scaled_out: Optional[torch.Tensor] = None,
+                  alpha: float = 1.0) -> None:
+    """y = rmsnorm(acc) * w for the float32 rows of ``acc``; y goes to ``x_out`` (float32), ``h_out`` (any
+    storage type) and, times ``alpha``, to ``scaled_out`` (float32), whichever are given (each may be ``acc``)."""
+    _need(acc, "acc", torch.float32); _need(w, "w", torch.float32)
+    n, d = acc.shape
+    if w.numel() != d:
+        raise KernelError("postnorm_rows: weight size")
+    for t, nm, dt in ((x_out, "x_out", torch.float32), (h_out, "h_out", None), (scaled_out, "scaled_out", torch.float32)):
+        if t is not None:
+            _need(t, nm, dt)
+            if tuple(t.shape) != (n, d):
+                raise KernelError(f"postnorm_rows: {nm} shape")
+    if n > MAX_STEP_ROWS:
+        raise KernelError("postnorm_rows: too many rows")
+    code = dtype_code(h_out.dtype) if h_out is not None else F32
+    _run("postnorm_rows", load_library("rowwise").kp_postnorm_rows, _ptr(acc), _ptr(w), _ptr(x_out), _ptr(h_out),
+         _ptr(scaled_out), n, d, ctypes.c_float(eps), ctypes.c_float(alpha), code, STREAM)
+
+
+def scale_cast(x: torch.Tensor, h_out: Optional[torch.Tensor], scaled_out: torch.Tensor, alpha: float) -> None:
+    """h_out = x in h_out's type (if given), scaled_out = alpha * x (float32)."""
+    _need(x, "x", torch.float32); _need(scaled_out, "scaled_out", torch.float32)
+    if h_out is not None:
+        _need(h_out, "h_out")
+        if h_out.numel() != x.numel():
+            raise KernelError("scale_cast: size mismatch")
+    if scaled_out.numel() != x.numel():
+        raise KernelError("scale_cast: size mismatch")
+    code = dtype_code(h_out.dtype) if h_out is not None else F32
+    _run("scale_cast", load_library("rowwise").kp_scale_cast, _ptr(x), _ptr(h_out), _ptr(scaled_out),
+         ctypes.c_longlong(x.numel()), ctypes.c_float(alpha), code, STREAM)
+
+
+def sigmoid_gate(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """o *= sigmoid(g), element by element; both 2-D with contiguous rows (``g`` may be columns of a wider tensor)."""
+    _need(o, "o", contiguous=False); _need(g, "g", o.dtype, contiguous=False)
+    if o.shape != g.shape:
+        raise KernelError("sigmoid_gate: shape mismatch")
+    _run("sigmoid_gate", load_library("rowwise").kp_sigmoid_gate, _ptr(o), _rows_2d(o, "o"), _ptr(g), _rows_2d(g, "g"),
+         o.shape[0], o.shape[1], dtype_code(o.dtype), STREAM)
+    return o
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
@@ -402,15 +458,22 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
                     cos_tab: Optional[torch.Tensor], sin_tab: Optional[torch.Tensor], rotary_dim: int,
                     interleaved: bool, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
                     q_out: Optional[torch.Tensor], cache: Optional[torch.Tensor], page_size: int, H: int, G: int,
-                    hd: int) -> Optional[torch.Tensor]:
+                    hd: int, v_col: Optional[int] = None) -> Optional[torch.Tensor]:
     """Norm + rotate q and k; write q to ``q_out`` and, if ``cache`` is given,
     k and v to their pages.  ``cache`` is one layer's [pages, 2, G, page_size, hd].
-    With ``q_out`` None, q and k are changed in place and no cache is written."""
+    With ``q_out`` None, q and k are changed in place and no cache is written.
+    ``v_col``: the column of a row at which the values start (default: behind the keys, ``(H + G) * hd``;
+    ``H * hd`` makes the values the key projections themselves, before norm and rotation).  Columns behind
+    q, k and v are left alone."""
     _need(qkv, "qkv", contiguous=False)
     _need(positions, "positions", torch.int32)
     n = qkv.shape[0]
-    if qkv.shape[1] != (H + 2 * G) * hd:
+    if v_col is None:
+        v_col = (H + G) * hd
+    if qkv.shape[1] < (H + G) * hd or not (0 <= v_col <= qkv.shape[1] - G * hd):
         raise KernelError("qk_norm_rope_kv: shape mismatch")
+    if q_out is None and v_col < (H + G) * hd:
+        raise KernelError("qk_norm_rope_kv: the in-place form would change the values it shares with the keys")
     if q_out is not None:
         _need(q_out, "q_out", qkv.dtype, contiguous=False)
         if q_out.shape != (n, H * hd):
@@ -436,13 +499,14 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
                                   _ptr(cos_tab), _ptr(sin_tab), rotary_dim, int(interleaved), _ptr(positions),
                                   _ptr(slot_map), _ptr(q_out), 0 if q_out is None else _rows_2d(q_out, "q_out"), _ptr(cache),
                                   page_size,
-                                  n, H, G, hd, int(write_kv), dtype_code(qkv.dtype), STREAM)
+                                  n, H, G, hd, int(write_kv), int(v_col), dtype_code(qkv.dtype), STREAM)
     return q_out
 
 
 def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                    positions: torch.Tensor, out: torch.Tensor, scale: float, window: Optional[int],
-                   page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+                   page_size: int, H: int, G: int, hd: int, block: Optional[int] = None) -> torch.Tensor:
+    """``block``: a row reads no key from before the start of its own block of that many positions."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32)
@@ -450,10 +514,9 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
     if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
         raise KernelError("attention_rows: shape mismatch")
     lib = load_library("attention")
-    _run("attention_rows", lib.kp_attention_rows, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
-                                 _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"),
-                                 ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
-                                 dtype_code(q.dtype), STREAM)
+    _run("attention_rows", lib.kp_attention_rows_masked, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
+         block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
+         int(window or 0), int(block or 0), page_size, n, H, G, hd, dtype_code(q.dtype), STREAM)
     return out
 
 
@@ -469,9 +532,11 @@ def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
-                    window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+                    window: Optional[int], page_size: int, H: int, G: int, hd: int,
+                    block: Optional[int] = None) -> torch.Tensor:
     """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
-    must cover the largest position of the batch; ``scratch`` is float32."""
+    must cover the largest position of the batch; ``scratch`` is float32.
+    ``block``: a row reads no key from before the start of its own block of that many positions."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
@@ -481,7 +546,7 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
         raise KernelError("attention_split: scratch too small")
     lib = load_library("attention_decode")
-    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
+    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0 and not block:
         # tensor-core chunk pass over smaller chunks, then the same merge
         parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
         _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma, 
@@ -492,10 +557,10 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
         _run("attention_merge", lib.kp_attention_merge, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
                                       SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
-    _run("attention_split", lib.kp_attention_split, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
-                                  _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
-                                  n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
-                                  dtype_code(q.dtype), STREAM)
+    _run("attention_split", lib.kp_attention_split_masked, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
+         block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
+         n_chunks, ctypes.c_float(scale), int(window or 0), int(block or 0), page_size, n, H, G, hd,
+         dtype_code(q.dtype), STREAM)
     LAUNCHES[0] += 1
     return out
 
@@ -598,7 +663,7 @@ def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, swiglu: bool = False, split: bool = True) -> torch.Tensor:
+            accumulate: bool = False, swiglu: bool = False, split: bool = True, activation: str = "silu") -> torch.Tensor:
     """out = a @ w.T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); with
     ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up.  With ``split`` a product of 17 to
     1024 rows is cut along K where that brings fewer bytes into the busiest SM (the parts of a tile are a
@@ -614,7 +679,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         _need(bias, "bias", torch.float32)
         if bias.numel() != N:
             raise KernelError("gemm_tc: bias size")
-    epi = _skinny_epilogue(out, accumulate, swiglu)
+    epi = _skinny_epilogue(out, accumulate, swiglu) | (_fused_activation(activation) << 8 if swiglu else 0)
     lib = load_library("gemm_tc")
     _run("gemm_tc", lib.kp_gemm_tc_split, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
          _rows_2d(out, "out"), M, N, K, epi, 1 if split else 0, STREAM, tag=f" {N}x{K}",
@@ -678,6 +743,15 @@ def gemm_stream_conv_step(a: torch.Tensor, w_in: torch.Tensor, bias: Optional[to
     return out
 
 
+FUSED_ACTIVATIONS = ("silu", "relu")     # what the products' gated epilogues compute themselves
+
+
+def _fused_activation(name: str) -> int:
+    if name not in FUSED_ACTIVATIONS:
+        raise KernelError(f"the gated epilogue computes {' or '.join(FUSED_ACTIVATIONS)}, not '{name}'")
+    return activation_code(name)
+
+
 def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
     if swiglu:
         if out.dtype != torch.bfloat16:
@@ -695,7 +769,7 @@ def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+                accumulate: bool = False, swiglu: bool = False, activation: str = "silu") -> torch.Tensor:
     """out = a @ w.T (+ bias) for up to 64 rows of bfloat16 ``a``.  With
     ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
@@ -712,7 +786,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     if swiglu:
         if out.dtype != torch.bfloat16:
             raise KernelError("gemm_skinny: the SwiGLU epilogue writes bfloat16")
-        epi = EPI_SWIGLU
+        epi = EPI_SWIGLU | (_fused_activation(activation) << 8)
     elif accumulate:
         if out.dtype != torch.float32:
             raise KernelError("gemm_skinny: accumulation needs a float32 output")
@@ -731,4 +805,54 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     lib = load_library("gemm_skinny")
     _run("gemm_skinny", lib.kp_gemm_skinny, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
          _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
+    return out
+
+
+# ------------------------------------------------------------------ mixture of experts
+
+MOE_MAX_TOP = 32           # experts a row can use
+MOE_MAX_EXPERTS = 1536     # experts the routing kernels hold in shared memory
+
+
+def moe_layout_ints(n: int, E: int, top: int) -> int:
+    """int32 words of the device-side layout of one step (see :func:`moe_route`)."""
+    return 2 * (E + 1) + 2 * n * top
+
+
+def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.Tensor, layout: torch.Tensor) -> None:
+    """Router logits [n, E] (float32) -> the ``top`` experts of every row (``idx`` int32 [n, top], largest logit
+    first, the lower index on ties), their weights (softmax over the chosen logits; float32 [n, top]) and the
+    layout of the (row, choice) pairs by expert (``layout``, int32, :func:`moe_layout_ints` words), which the
+    grouped products read.  Nothing returns to the host."""
+    _need(logits, "logits", torch.float32); _need(idx, "idx", torch.int32); _need(weights, "weights", torch.float32)
+    _need(layout, "layout", torch.int32)
+    n, E = logits.shape
+    if not (1 <= top <= min(E, MOE_MAX_TOP)) or E > MOE_MAX_EXPERTS:
+        raise KernelError(f"moe_route: top={top} of {E} experts is not supported (top <= {MOE_MAX_TOP}, experts <= {MOE_MAX_EXPERTS})")
+    if idx.numel() != n * top or weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
+        raise KernelError("moe_route: output sizes")
+    _run("moe_route", load_library("moe").kp_moe_route, _ptr(logits), n, E, top, _ptr(idx), _ptr(weights), _ptr(layout), STREAM)
+    LAUNCHES[0] += 1
+
+
+def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, layout: torch.Tensor,
+                weights: torch.Tensor, top: int, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """out[r] += sum_j weights[r, j] * Wd_e (act(Wg_e h[r]) * (Wu_e h[r])), e = the j-th expert of row r as laid out
+    by :func:`moe_route`.  ``w_gate_up``: [E, 2 ff, d] (gate rows, then up rows); ``w_down``: [E, d, ff]; ``out``
+    float32 [n, d].  bfloat16 operands run on the tensor cores, float32 ones on the CUDA cores in true 32-bit."""
+    _need(h, "h", contiguous=False); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
+    _need(layout, "layout", torch.int32); _need(weights, "weights", torch.float32); _need(out, "out", torch.float32)
+    n, d = h.shape
+    E, ff2, d2 = w_gate_up.shape
+    ff = ff2 // 2
+    if d2 != d or ff2 != 2 * ff or tuple(w_down.shape) != (E, d, ff) or tuple(out.shape) != (n, d):
+        raise KernelError("moe_experts: shape mismatch")
+    if weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
+        raise KernelError("moe_experts: routing tables do not fit")
+    act = torch.empty((n * top, ff), dtype=h.dtype, device=h.device)
+    y = torch.empty((n * top, d), dtype=torch.float32, device=h.device)
+    _run("moe_experts", load_library("moe").kp_moe_experts, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate_up), _ptr(w_down), _ptr(layout),
+         _ptr(weights), _ptr(act), _ptr(y), _ptr(out), n, E, top, d, ff, activation_code(activation), dtype_code(h.dtype),
+         STREAM, tag=f" {E}x{ff}x{d}", work=(6 * n * top * ff * d, 0))
+    LAUNCHES[0] += 2
     return out

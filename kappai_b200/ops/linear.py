@@ -46,16 +46,18 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return K.gemm_nt_simt(a, w, out, bias, accumulate)
 
 
-def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(a @ Wg.T) * (a @ Wu.T)`` with ``w_gate_up = [Wg; Wu]``; one fused
-    kernel where there is one for the shape, else product then activation.
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  activation: str = "silu") -> torch.Tensor:
+    """``act(a @ Wg.T) * (a @ Wu.T)`` with ``w_gate_up = [Wg; Wu]`` and act = silu (or ``activation``); one
+    fused kernel where there is one for the shape, else product then activation.
     Gate and up are rounded to the storage type before the activation either way."""
     ff = w_gate_up.shape[0] // 2
     act = torch.empty((a.shape[0], ff), dtype=a.dtype, device=a.device)
-    tc = K.tc_ok(a, w_gate_up)
-    if K.skinny_ok(a, w_gate_up) and not (tc and K.tc_pays_for_few_rows(a.shape[0], w_gate_up.shape[0], True)):
-        return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True)
+    fused = activation in K.FUSED_ACTIVATIONS
+    tc = fused and K.tc_ok(a, w_gate_up)
+    if fused and K.skinny_ok(a, w_gate_up) and not (tc and K.tc_pays_for_few_rows(a.shape[0], w_gate_up.shape[0], True)):
+        return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True, activation=activation)
     if tc:
-        return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True)
+        return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True, activation=activation)
     gu = linear(a, w_gate_up, bias)
-    return K.swiglu(gu, act)
+    return K.swiglu(gu, act, activation)

@@ -9,8 +9,18 @@ values into the cache; causal softmax attention with ``scale`` over the keys
 ``out = attn Wo^T`` added to the residual (src/models/lfm.c:51,
 src/recipe/builders.c:381).
 
+Variants, each a parameter: ``values`` = ``"keys"`` leaves the value matrix out
+and takes as values the key projections as they leave the product, before the
+key norm and the rotation; ``block`` (a number of positions) lets a row read no
+key from before the start of its own block, blocks being counted from position
+0 of the sequence, whatever the portions a prompt is run in; ``gate`` =
+``"sigmoid"`` multiplies the concatenated heads, element by element, with
+``sigmoid(h Wg^T)`` in front of the output matrix (Wg rides in the same product
+as q and k).
+
 Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
-scale, qk_norm_eps (None: no q/k norm), window (None: all keys), position (a
+scale, qk_norm_eps (None: no q/k norm), window (None: all keys), block (None),
+values ("projection" | "keys"), gate (None | "sigmoid"), position (a
 ``position`` PartSpec), bias.
 """
 from __future__ import annotations
@@ -88,11 +98,24 @@ class Attention(Part):
         self.qk_norm_eps: Optional[float] = None if eps is None else float(eps)
         self.window: Optional[int] = self._p("window", None)
         self.bias = bool(self._p("bias", False))
+        self.block: Optional[int] = self._p("block", None)
+        if self.block is not None and int(self.block) < 1:
+            raise ConfigError(f"attention: block={self.block} must be a positive number of positions")
+        values = self._p("values", "projection")
+        if values not in ("projection", "keys"):
+            raise ConfigError(f"attention: values='{values}' (expected 'projection' or 'keys')")
+        self.values_are_keys = values == "keys"
+        gate = self._p("gate", None)
+        if gate not in (None, "sigmoid"):
+            raise ConfigError(f"attention: gate='{gate}' (expected 'sigmoid' or none)")
+        self.gated = gate is not None
+        if self.bias and (self.values_are_keys or self.gated):
+            raise ConfigError("attention: biases are not combined with values='keys' or a gate")
         if self.H < 1 or self.G < 1 or self.H % self.G:
             raise ConfigError(f"attention: num_heads={self.H} must be a multiple of num_kv_heads={self.G}")
-        if self.hd % 16 or not (16 <= self.hd <= 256):
+        if self.hd % 2 or not (2 <= self.hd <= 256):
             raise ConfigError(f"attention: head_dim={self.hd} is not supported by the kernels "
-                              "(a multiple of 16 from 16 to 256)")
+                              "(an even number from 2 to 256)")
         pos = self._p("position", None)
         if pos is None:
             pos = PartSpec("none")
@@ -100,7 +123,11 @@ class Attention(Part):
             pos = PartSpec(**pos)
         self.position = make_part("position", pos, env)
         self.graph_safe = bool(self.position.graph_safe)     # a position part that reads host values keeps it eager
-        self.split_ok = self.H // self.G <= K.SPLIT_MAX_RATIO
+        if self.values_are_keys and not hasattr(self.position, "fused_rotary"):
+            raise ConfigError("attention: values='keys' needs a position encoding that runs in the fused q/k kernel")
+        # (the split-key kernel reads keys 16 bytes at a time and shares a kv head among at most 8 query heads;
+        # other shapes take the general kernel for every row)
+        self.split_ok = self.H // self.G <= K.SPLIT_MAX_RATIO and self.hd % 16 == 0
         self.step_tables_key = ("attention_tiles", self.split_ok)
 
     def step_tables(self, segs):
@@ -109,7 +136,11 @@ class Attention(Part):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         d, H, G, hd = self.d, self.H, self.G, self.hd
         s = {"q_proj.weight": WeightSpec((H * hd, d)), "k_proj.weight": WeightSpec((G * hd, d)),
-             "v_proj.weight": WeightSpec((G * hd, d)), "out_proj.weight": WeightSpec((d, H * hd))}
+             "out_proj.weight": WeightSpec((d, H * hd))}
+        if not self.values_are_keys:
+            s["v_proj.weight"] = WeightSpec((G * hd, d))
+        if self.gated:
+            s["gate_proj.weight"] = WeightSpec((H * hd, d))
         if self.qk_norm_eps is not None:
             s["q_norm.weight"] = WeightSpec((hd,), "norm")
             s["k_norm.weight"] = WeightSpec((hd,), "norm")
@@ -119,7 +150,15 @@ class Attention(Part):
         return s
 
     def bind(self, w):
-        self.w_qkv = torch.cat([w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"]], 0).contiguous()
+        # one product for everything that reads the layer's input: rows [q | k | v (if it has a matrix) | gate]
+        rows = [w["q_proj.weight"], w["k_proj.weight"]]
+        if not self.values_are_keys:
+            rows.append(w["v_proj.weight"])
+        self.gate_col = sum(r.shape[0] for r in rows)
+        if self.gated:
+            rows.append(w["gate_proj.weight"])
+        self.w_qkv = torch.cat(rows, 0).contiguous()
+        self.v_col = self.H * self.hd if self.values_are_keys else (self.H + self.G) * self.hd
         self.w_o = w["out_proj.weight"].contiguous()
         self.b_qkv = self.b_o = None
         if self.bias:
@@ -143,7 +182,7 @@ class Attention(Part):
         if hasattr(self.position, "fused_rotary"):
             cos, sin, rot, inter = self.position.fused_rotary()
             K.qk_norm_rope_kv(qkv, self.q_w, self.k_w, self.qk_norm_eps or 0.0, cos, sin, rot, inter,
-                              ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd)
+                              ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd, self.v_col)
         else:
             # a position encoding of its own: norm in place, let it change q and k, then scatter
             if self.q_w is not None:
@@ -154,12 +193,13 @@ class Attention(Part):
                               view.page_size, H, G, hd)
         o = torch.empty_like(q)
         tiles = ctx.tables.get(self.step_tables_key)
+        tiled_ok = self.block is None            # the tiled prompt kernels know windows, not blocks of positions
         if self.split_ok and (tiles is None or q.dtype == torch.float32):
             # rows that each read a long cache (decode): split the keys over many CTAs.  The 32-bit path
             # takes this kernel for every row, whatever the length of its segment: its chunks lie at absolute
             # multiples of 256 keys and are summed in order, so a row's bits do not depend on how the step was cut.
             self._split(q, o, ctx, view, cache, ctx.n_rows)
-        elif tiles is not None and K.attention_prefill_ok(q, hd):
+        elif tiles is not None and tiled_ok and K.attention_prefill_ok(q, hd):
             lead = tiles.n_short_rows
             if lead and self.split_ok:
                 # decoded tokens beside prompt portions: the decoded rows lead the batch and go to the split
@@ -175,8 +215,15 @@ class Attention(Part):
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
                                     tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big)
         else:
-            K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
-                             self.window, view.page_size, H, G, hd)
+            lead = tiles.n_short_rows if tiles is not None else 0
+            if lead and self.split_ok:
+                self._split(q, o, ctx, view, cache, lead)
+            else:
+                lead = 0
+            K.attention_rows(q[lead:], cache.tensor, view.block_table, ctx.row_seg[lead:], ctx.positions[lead:], o[lead:],
+                             self.scale, self.window, view.page_size, H, G, hd, self.block)
+        if self.gated:
+            K.sigmoid_gate(o, qkv[:, self.gate_col:self.gate_col + H * hd])
         linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
 
 
@@ -196,7 +243,7 @@ class Attention(Part):
                              device=q.device)
             self.env.shared["attn_scratch"] = ws
         K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
-                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd)
+                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block)
 
 
 register_part("mixer", "attention", Attention)

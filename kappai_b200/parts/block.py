@@ -3,9 +3,20 @@
 ``prenorm_residual``: ``x += mixer(norm1(x)); x += ffn(norm2(x))``
 (src/models/lfm.c:7-53 followed by src/recipe/builders.c:378-388).  The
 residual ``x`` is float32 and is updated in place.
+
+``postnorm_residual``: ``x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ffn(x))``:
+the sublayers read ``x`` itself (in the compute type), the norm comes after the
+sum, and ``alpha`` (parameter, default 1) weighs the residual branch.  A layer
+without a feed-forward has the first half only.  The sum and the norm are
+float32; one kernel norms a sum and writes what the next sublayer needs (its
+input in the compute type and ``alpha`` times the new residual to add into), so
+a layer costs two row-wise launches, as a pre-norm layer does.
 """
 from __future__ import annotations
 
+import torch
+
+from ..ops import kernels as K
 from .base import Part, register_part
 
 
@@ -23,4 +34,53 @@ class PreNormResidualBlock(Part):
             self.ffn.forward(self.ffn_norm.forward(x) if self.ffn_norm is not None else x, x, ctx)
 
 
+class PostNormResidualBlock(Part):
+    category = "block"
+    graph_safe = True
+
+    def __init__(self, params, env):
+        super().__init__(params, env)
+        self.alpha = float(self._p("alpha", 1.0))
+
+    def assemble(self, mixer, ffn, mixer_norm, ffn_norm):
+        if mixer_norm is None or (ffn is not None and ffn_norm is None):
+            raise ValueError("postnorm_residual: every sublayer needs the norm that follows its sum")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+        return self
+
+    def _enter(self, x, ctx):
+        """The sublayer input (x in the compute type) and alpha * x: left by the block before this one for
+        this very residual, or made here."""
+        carry = getattr(ctx, "postnorm_carry", None)
+        ctx.postnorm_carry = None
+        if carry is not None and carry[0] is x and carry[1] == self.alpha:
+            return carry[2], carry[3]
+        acc = torch.empty_like(x)
+        if self.env.dtype == torch.float32:
+            K.scale_cast(x, None, acc, self.alpha)
+            return x, acc
+        h = torch.empty(x.shape, dtype=self.env.dtype, device=x.device)
+        K.scale_cast(x, h, acc, self.alpha)
+        return h, acc
+
+    def forward(self, x, ctx, cache):
+        f32 = self.env.dtype == torch.float32
+        h, acc = self._enter(x, ctx)
+        self.mixer.forward(h, acc, ctx, cache)
+        # what the sublayer after this norm reads and adds into; in 32-bit its input is the residual itself
+        h2 = x if f32 else (h if h is not x else torch.empty(x.shape, dtype=self.env.dtype, device=x.device))
+        if self.ffn is not None:
+            n1 = self.mixer_norm
+            K.postnorm_rows(acc, n1.weight, n1.eps, x_out=x if f32 else None, h_out=None if f32 else h2,
+                            scaled_out=acc, alpha=self.alpha)
+            self.ffn.forward(h2, acc, ctx)
+            last = self.ffn_norm
+        else:
+            last = self.mixer_norm
+        # the new residual, and with it the entry of a post-norm block that may follow
+        K.postnorm_rows(acc, last.weight, last.eps, x_out=x, h_out=None if f32 else h2, scaled_out=acc, alpha=self.alpha)
+        ctx.postnorm_carry = (x, self.alpha, x if f32 else h2, acc)
+
+
 register_part("block", "prenorm_residual", PreNormResidualBlock)
+register_part("block", "postnorm_residual", PostNormResidualBlock)

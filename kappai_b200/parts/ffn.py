@@ -5,7 +5,14 @@ as one product against [Wg; Wu], gate rows first (src/recipe/builders.c:344-388,
 src/model.c:1575-1610); ``silu(g) = g / (1 + exp(-g))``
 (src/backend/cpu/quants.h:369-371).
 
-Params: hidden_size, intermediate_size, bias.
+Params: hidden_size, intermediate_size, bias, activation (``silu`` by default;
+``relu`` and ``gelu_tanh`` make the same unit with another function on the gate:
+kind ``glu``).
+
+``moe``: a mixture of ``num_experts`` such units without biases, of which every
+row uses the ``top`` with the largest router logits ``z = h Wr^T + b`` (float32),
+weighted by the softmax over those ``top`` logits alone; see csrc/moe.cu.
+Params: hidden_size, expert_size, num_experts, top, activation, router_bias.
 """
 from __future__ import annotations
 
@@ -15,6 +22,7 @@ import torch
 
 from ..ops import kernels as K
 from ..ops.linear import linear, linear_swiglu
+from ..config.schema import ConfigError
 from .base import Part, WeightSpec, register_part
 
 
@@ -27,6 +35,8 @@ class SwiGLU(Part):
         self.d = int(self._p("hidden_size"))
         self.ff = int(self._p("intermediate_size"))
         self.bias = bool(self._p("bias", False))
+        self.activation = str(self._p("activation", "silu"))
+        K.activation_code(self.activation)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         s = {"gate_proj.weight": WeightSpec((self.ff, self.d)), "up_proj.weight": WeightSpec((self.ff, self.d)),
@@ -46,8 +56,56 @@ class SwiGLU(Part):
             self.b_down = w["down_proj.bias"].float().contiguous()
 
     def forward(self, h, residual, ctx):
-        act = linear_swiglu(h, self.w_gu, self.b_gu)
+        act = linear_swiglu(h, self.w_gu, self.b_gu, self.activation)
         linear(act, self.w_down, self.b_down, out=residual, accumulate=True)
 
 
+class MixtureOfExperts(Part):
+    category = "feed_forward"
+    graph_safe = True          # rows meet their experts on the device; the host sees none of it
+
+    def __init__(self, params, env):
+        super().__init__(params, env)
+        self.d = int(self._p("hidden_size"))
+        self.ff = int(self._p("expert_size"))
+        self.E = int(self._p("num_experts"))
+        self.top = int(self._p("top"))
+        self.activation = str(self._p("activation", "silu"))
+        self.router_bias = bool(self._p("router_bias", True))
+        K.activation_code(self.activation)
+        if self.E < 1 or not (1 <= self.top <= self.E):
+            raise ConfigError(f"moe: top={self.top} must lie between 1 and num_experts={self.E}")
+        if self.top > K.MOE_MAX_TOP or self.E > K.MOE_MAX_EXPERTS:
+            raise ConfigError(f"moe: the kernels take top <= {K.MOE_MAX_TOP} and num_experts <= {K.MOE_MAX_EXPERTS}")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        s = {"router.weight": WeightSpec((self.E, self.d))}
+        if self.router_bias:
+            s["router.bias"] = WeightSpec((self.E,), "bias")
+        for e in range(self.E):
+            s[f"experts.{e}.gate_proj.weight"] = WeightSpec((self.ff, self.d))
+            s[f"experts.{e}.up_proj.weight"] = WeightSpec((self.ff, self.d))
+            s[f"experts.{e}.down_proj.weight"] = WeightSpec((self.d, self.ff))
+        return s
+
+    def bind(self, w):
+        # the router is 32-bit whatever the storage of the rest
+        self.w_router = w["router.weight"].to(torch.float32).contiguous()
+        self.b_router = w["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
+        self.w_gu = torch.stack([torch.cat([w[f"experts.{e}.gate_proj.weight"], w[f"experts.{e}.up_proj.weight"]], 0)
+                                 for e in range(self.E)]).contiguous()                       # [E, 2 ff, d]
+        self.w_down = torch.stack([w[f"experts.{e}.down_proj.weight"] for e in range(self.E)]).contiguous()   # [E, d, ff]
+
+    def forward(self, h, residual, ctx):
+        n = h.shape[0]
+        logits = linear(h, self.w_router, self.b_router, out_dtype=torch.float32)
+        idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
+        layout = torch.empty(K.moe_layout_ints(n, self.E, self.top), dtype=torch.int32, device=h.device)
+        K.moe_route(logits, self.top, idx, weights, layout)
+        K.moe_experts(h, self.w_gu, self.w_down, layout, weights, self.top, residual, self.activation)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "glu", SwiGLU)
+register_part("feed_forward", "moe", MixtureOfExperts)

@@ -7,6 +7,11 @@ shares one table between all layers with the same sizes, src/compute.c:80-102,
 and so does this).  ``pairing`` is ``neox`` (j, j + rotary_dim/2) or
 ``interleaved`` (2j, 2j+1) (src/backend/cpu/scalar/core.c:66-84); ``rotary_dim``
 may be smaller than the head size (the rest of the head is left as it is).
+``scaling`` (optional; keys ``factor``, ``low``, ``high``, ``original``) rescales the
+frequencies by their wavelength ``l = 2 pi / f``: a frequency with
+``l < original / high`` is kept, one with ``l > original / low`` is divided by
+``factor``, and between the two, with ``s = (original / l - low) / (high - low)``,
+it becomes ``(1 - s) f / factor + s f``.
 
 ``none``: no rotation.
 """
@@ -17,6 +22,18 @@ import torch
 
 from ..config.schema import ConfigError
 from .base import Part, register_part
+
+
+def scaled_frequencies(f: np.ndarray, scaling) -> np.ndarray:
+    """Rotary frequencies rescaled by wavelength (see the module's text); ``scaling`` is
+    (factor, low, high, original) or None."""
+    if scaling is None:
+        return f
+    factor, low, high, original = scaling
+    lam = 2.0 * np.pi / f
+    s = (original / lam - low) / (high - low)
+    blend = (1.0 - s) * f / factor + s * f
+    return np.where(lam < original / high, f, np.where(lam > original / low, f / factor, blend))
 
 
 class RotaryEncoding(Part):
@@ -33,10 +50,21 @@ class RotaryEncoding(Part):
         if self.rotary_dim < 2 or self.rotary_dim % 2:
             raise ConfigError(f"rope: rotary_dim={self.rotary_dim} must be even and positive")
         self.interleaved = pairing == "interleaved"
-        key = ("rope", self.rotary_dim, self.theta, env.max_positions)
+        scaling = self._p("scaling", None)
+        self.scaling = None
+        if scaling:
+            try:
+                self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            except (KeyError, TypeError, ValueError):
+                raise ConfigError("rope: scaling needs the numbers factor, low, high and original") from None
+            factor, low, high, original = self.scaling
+            if factor <= 0 or original <= 0 or low <= 0 or high <= low:
+                raise ConfigError("rope: scaling wants factor, original, low > 0 and high > low")
+        key = ("rope", self.rotary_dim, self.theta, self.scaling, env.max_positions)
         if key not in env.shared:
             half = self.rotary_dim // 2
-            inv = np.power(self.theta, -2.0 * np.arange(half, dtype=np.float64) / self.rotary_dim)
+            inv = scaled_frequencies(
+                np.power(self.theta, -2.0 * np.arange(half, dtype=np.float64) / self.rotary_dim), self.scaling)
             ang = np.arange(env.max_positions, dtype=np.float64)[:, None] * inv[None, :]
             env.shared[key] = (torch.from_numpy(np.cos(ang).astype(np.float32)).to(env.device),
                                torch.from_numpy(np.sin(ang).astype(np.float32)).to(env.device))
