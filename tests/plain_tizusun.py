@@ -182,15 +182,21 @@ class PlainTizusun:
     def sub(self, prefix):
         return {k[len(prefix):]: v for k, v in self.w.items() if k.startswith(prefix)}
 
-    def feed_forward(self, h, i):
+    def feed_forward(self, h, i, margins=None):
         mlp = self.cfg["layers"][i]["mlp"]
         w = self.sub(f"l{i}.mlp.")
         if mlp["kind"] == "dense":
             return gated_unit(h, w["gate"], w["up"], w["down"], "relu")
-        return mixture(h, w, mlp["router"]["experts"], mlp["router"]["top"], "silu")
+        E, top = mlp["router"]["experts"], mlp["router"]["top"]
+        if margins is not None and top < E:
+            z = np.sort(h @ w["router"].T + w["router.b"], axis=-1)[:, ::-1]
+            margins.append(z[:, top - 1] - z[:, top])
+        return mixture(h, w, E, top, "silu")
 
-    def forward(self, tokens, residuals=None):
-        """Logits [T, vocab] of one whole sequence; ``residuals`` (a list) gets x after every layer."""
+    def forward(self, tokens, residuals=None, margins=None):
+        """Logits [T, vocab] of one whole sequence; ``residuals`` (a list) gets x after every layer,
+        ``margins`` (a list) for every mixture layer the gap, token by token, between the last chosen
+        router logit and the first one left out."""
         c = self.cfg
         eps, alpha = c["norm"]["eps"], c["postln_alpha"]
         pos = np.arange(len(tokens))
@@ -200,7 +206,7 @@ class PlainTizusun:
             x = rms_norm(alpha * x + attention_mixer(x, self.sub(f"l{i}.mix."), layer["mixer"], eps, pos),
                          self.w[f"l{i}.norm1"], eps)
             if layer.get("mlp") is not None:
-                x = rms_norm(alpha * x + self.feed_forward(x, i), self.w[f"l{i}.norm2"], eps)
+                x = rms_norm(alpha * x + self.feed_forward(x, i, margins), self.w[f"l{i}.norm2"], eps)
             if residuals is not None:
                 residuals.append(x.copy())
         return rms_norm(x, self.w["final.norm"], eps) @ self.w["head"].T

@@ -131,7 +131,8 @@ def run_trace(model_dir, dtype, trace, out_dir, max_tokens, page_size=None, time
         if proc.poll() is None:
             proc.kill()
     with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+        cfg = json.load(f)
+        vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     out = {}
     for st, rows in zip(trace.steps, trace.rows):
         path = os.path.join(out_dir, f"{st['step']}.f32")
