@@ -239,6 +239,8 @@ def _requests(plain, lengths, seed, min_margin=0.0):
 
 LENGTHS = {"P": [70, 3, 121, 49], "Q": [90, 41, 2, 130], "R": [77, 20, 101], "S": [330, 64, 201, 129]}
 PROMPTS = {"P": [30, 1, 60, 48], "Q": [50, 40, 1, 100], "R": [40, 19, 60], "S": [220, 3, 101, 128]}
+BF16_REL_RMS = 0.03    # bound on a row's 16-bit error (rms over the vocabulary / the row's spread) for 95 % of the rows, twice
+                       # that for all (measured: median 0.3 to 1.2 %, 95 % of rows below 2.2 %, worst row 3.9 %)
 MARGIN = 0.12          # router logits here have a spread of about 3; 16-bit inputs move them by about 0.01
 
 
@@ -264,7 +266,21 @@ def test_every_cut_agrees_with_plain(name, page_size, dtype, tiz_dirs, tiz_plain
     R.mixed(tr, reqs, prompt_len, seed=5, max_live=4, page=page, max_tokens=max_tokens)
     assert max(len(s["entries"]) for s in tr.steps[b:]) >= 2
     out = R.run_trace(tiz_dirs[name], dtype, tr, str(tmp_path / "out"), max_tokens, page_size)
-    worst = R.compare(tr, out, expected, tol, f"{name}/{dtype}")
+    if dtype == "bfloat16":
+        # 16-bit: the error of a row as a root mean square over the vocabulary, in units of the row's spread; rounding
+        # alone gives a few per cent (these weights have unit gain: every sublayer moves the residual), a wrong key,
+        # page or expert gives tens
+        rel = []
+        for st, rows in zip(tr.steps, tr.rows):
+            for j, (rid, pos) in enumerate(rows):
+                e = expected[rid][pos]
+                rel.append((float(np.sqrt(np.mean((out[st["step"]][j] - e) ** 2)) / e.std()), st["step"], rid, pos))
+        r = np.array([x[0] for x in rel])
+        print(f"{name} bfloat16: relative rms error median {np.median(r):.4f}, 95 % {np.quantile(r, 0.95):.4f}, worst {r.max():.4f}")
+        assert np.quantile(r, 0.95) <= BF16_REL_RMS and r.max() <= 2 * BF16_REL_RMS, max(rel)
+        worst = float(r.max())
+    else:
+        worst = R.compare(tr, out, expected, tol, f"{name}/{dtype}")
     stats = R.cache_stats(str(tmp_path / "out"))
     assert stats and all(g["reused"] > 0 and g["handed_out"] > g["pages"] for g in stats.values()), stats
     if dtype == "float32":
