@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(NW * 32)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                      int n_chunks, float scale, int window, int page_size, int H, int G) {
+                      int n_chunks, float scale, int window, int page_size, int H, int G, int block) {
     kp_pdl_begin_early_if(gridDim.z > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -152,7 +152,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
     const int chunk = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int R = H / G;
     const int pos = positions[row];
-    const int k_lo = window > 0 ? max(0, pos - window + 1) : 0, k_hi = pos;
+    const int k_lo = kp_key_lo(pos, window, block), k_hi = pos;
     const int c0 = chunk * CHUNK;
     if (c0 > k_hi || c0 + CHUNK - 1 < k_lo) return;
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(AR_THREADS)
 attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                        const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                       int n_chunks, float scale, int window, int page_size, int H, int G, int n_rows) {
+                       int n_chunks, float scale, int window, int page_size, int H, int G, int n_rows, int block) {
     kp_pdl_begin_early_if(n_rows > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -366,7 +366,7 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
                 c_kvh = rest % G;
                 c_row = rest / G;
                 const int pos = positions[c_row];
-                c_lo = window > 0 ? max(0, pos - window + 1) : 0;
+                c_lo = kp_key_lo(pos, window, block);
                 c_hi = pos;
                 const int c0 = c_chunk * AR_CHUNK;
                 valid = !(c0 > c_hi || c0 + AR_CHUNK - 1 < c_lo);
@@ -557,7 +557,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_rows,
                         const int* __restrict__ seg_pos, const int* __restrict__ tile_seg,
                         const int* __restrict__ tile_row0, bf16* __restrict__ out, int ldo, float scale, int window,
-                        int page_size, int H, int G) {
+                        int page_size, int H, int G, int block) {
     kp_pdl_begin();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [2][64][HD]
@@ -576,7 +576,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
 
     // keys any row of the tile may read
     const int k_hi_all = pos0 + n_rows - 1;
-    const int k_lo_all = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int k_lo_all = kp_key_lo(pos0, window, block);
     const int tile_lo = k_lo_all / AM_TILE, tile_hi = k_hi_all / AM_TILE;
 
     // this warp's 16 rows: rows r0 = warp*16 + g and r0 + 8
@@ -595,7 +595,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
             qf[ks][3] = *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8 + 2 * t);
         }
     }
-    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0, lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+    const int lo_a = kp_key_lo(pos_a, window, block), lo_b = kp_key_lo(pos_b, window, block);
 
     float o[HD / 8][4];
 #pragma unroll
@@ -621,7 +621,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
         const int t0 = kt * AM_TILE;
         // a warp whose rows all lie before this tile (causal) or after its window has nothing to do in it
         const int w_pos_hi = pos0 + min(warp * 16 + 15, n_rows - 1);
-        const int w_lo = window > 0 ? max(0, pos0 + warp * 16 - window + 1) : 0;
+        const int w_lo = kp_key_lo(pos0 + warp * 16, window, block);
         if (warp * 16 < n_rows && t0 <= w_pos_hi && t0 + AM_TILE - 1 >= w_lo) {
             float s[8][4];
             qk_tile<HD>(s, qf, Ks + buf * AM_TILE * HD, lane);
@@ -696,7 +696,7 @@ static int am_n_sm() {
 template <int HD, int NW>
 static int launch_split(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
                         int max_blocks, const int* row_seg, const int* positions, float* part_acc, float* part_ml,
-                        int n_chunks, float scale, int window, int page_size, int n, int H, int G, cudaStream_t s) {
+                        int n_chunks, float scale, int window, int block, int page_size, int n, int H, int G, cudaStream_t s) {
     const size_t smem = 1024 + (size_t)2 * NW * AM_TILE * HD * 2 + sizeof(float) * (NW * AM_RMAX * HD + 2 * NW * AM_RMAX) + 16;
     alignas(64) CUtensorMap tm = {};
     // tiles by TMA where the pages allow it (and the cache is known by its size), else by cp.async
@@ -718,7 +718,7 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
             const int sms = am_n_sm();
             kp_launch_pdl(attn_split_ring_kernel<HD>, dim3((unsigned)(items < sms ? items : sms)), dim3(AR_THREADS), rs, s, tm,
                           (const bf16*)q, ldq, block_table, max_blocks, row_seg, positions, part_acc, part_ml, n_chunks, scale,
-                          window, page_size, H, G, n);
+                          window, page_size, H, G, n, block);
             return kp_launch_status();
         }
     }
@@ -729,20 +729,20 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
     }
     kp_launch_pdl(kern, dim3(dim3(n_chunks, G, n)), dim3(NW * 32), smem, s, tm,
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
-        n_chunks, scale, window, page_size, H, G);
+        n_chunks, scale, window, page_size, H, G, block);
     return kp_launch_status();
 }
 
 template <int HD>
 static int launch_prefill(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
                           const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0, int n_tiles,
-                          void* out, int ldo, float scale, int window, int page_size, int H, int G, cudaStream_t s) {
+                          void* out, int ldo, float scale, int window, int block, int page_size, int H, int G, cudaStream_t s) {
     const size_t smem = (size_t)4 * AM_TILE * HD * 2;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     kp_launch_pdl(attn_prefill_mma_kernel<HD>, dim3(dim3(n_tiles, H)), dim3(128), smem, s, 
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-        (bf16*)out, ldo, scale, window, page_size, H, G);
+        (bf16*)out, ldo, scale, window, page_size, H, G, block);
     return kp_launch_status();
 }
 
@@ -751,10 +751,12 @@ extern "C" {
 // The chunk partials of the split pass (bfloat16, head size 64 or 128, H/G <= 8); chunks of `chunk_keys` keys
 // (64, 128 or 256), n_chunks of them, into `scratch` (n * H * n_chunks * (hd + 2) floats).  The caller runs the
 // merge of attention_decode.cu afterwards (kp_attention_merge, same chunk size) on the same scratch.
-int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table, int max_blocks,
-                           const int* row_seg, const int* positions, float* scratch, int n_chunks, int chunk_keys,
-                           float scale, int window, int page_size, int n, int H, int G, int hd, void* stream) {
+int kp_attention_split_mma_masked(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
+                                  int max_blocks, const int* row_seg, const int* positions, float* scratch, int n_chunks,
+                                  int chunk_keys, float scale, int window, int block, int page_size, int n, int H, int G,
+                                  int hd, void* stream) {
     if (n <= 0) return 0;
+    if (block < 0) return KP_ERR_BAD_ARG;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || H / G > AM_RMAX || page_size < 1 || n_chunks < 1 || n > 65535 ||
         G > 65535 || (ldq & 1) || (chunk_keys != 64 && chunk_keys != 128 && chunk_keys != 256))
         return KP_ERR_UNSUPPORTED;
@@ -763,7 +765,7 @@ int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long 
     cudaStream_t s = (cudaStream_t)stream;
 #define AM_SPLIT(HD, NW)                                                                                          \
     return launch_split<HD, NW>(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, part_acc, part_ml, \
-                                n_chunks, scale, window, page_size, n, H, G, s)
+                                n_chunks, scale, window, block, page_size, n, H, G, s)
     if (hd == 64) {
         if (chunk_keys == 64) AM_SPLIT(64, 1);
         if (chunk_keys == 128) AM_SPLIT(64, 2);
@@ -775,19 +777,36 @@ int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long 
 #undef AM_SPLIT
 }
 
+int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table, int max_blocks,
+                           const int* row_seg, const int* positions, float* scratch, int n_chunks, int chunk_keys,
+                           float scale, int window, int page_size, int n, int H, int G, int hd, void* stream) {
+    return kp_attention_split_mma_masked(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, scratch, n_chunks,
+                                         chunk_keys, scale, window, 0, page_size, n, H, G, hd, stream);
+}
+
 // tile_seg / tile_row0: for each tile of 64 rows its segment and its first row (device arrays, n_tiles long)
-int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                             const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
-                             int n_tiles, void* out, int ldo, float scale, int window, int page_size, int H, int G,
-                             int hd, void* stream) {
+// block: 0, or the size of the blocks of positions beyond whose start a row reads no key.
+int kp_attention_prefill_mma_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                                    const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
+                                    int n_tiles, void* out, int ldo, float scale, int window, int block, int page_size,
+                                    int H, int G, int hd, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (block < 0) return KP_ERR_BAD_ARG;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || page_size < 1 || H > 65535 || (ldq & 1) || (ldo & 1))
         return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return launch_prefill<64>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-                                            n_tiles, out, ldo, scale, window, page_size, H, G, s);
+                                            n_tiles, out, ldo, scale, window, block, page_size, H, G, s);
     return launch_prefill<128>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
-                               out, ldo, scale, window, page_size, H, G, s);
+                               out, ldo, scale, window, block, page_size, H, G, s);
+}
+
+int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                             const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
+                             int n_tiles, void* out, int ldo, float scale, int window, int page_size, int H, int G,
+                             int hd, void* stream) {
+    return kp_attention_prefill_mma_masked(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
+                                           n_tiles, out, ldo, scale, window, 0, page_size, H, G, hd, stream);
 }
 
 

@@ -55,6 +55,7 @@ struct AtArgs {
     const int* cu_rows; const int* seg_pos; const int* tile_seg; const int* tile_row0;
     bf16* out; int ldo;
     float scale; int window; int page_size; int H, G; int n_tiles;
+    int block;                                                  // 0, or rows read no key from before their own block of positions
 };
 
 // One piece of work: 128 rows (or the segment's last few) of one segment
@@ -70,7 +71,7 @@ __device__ __forceinline__ AtItem at_item(const AtArgs& p, int tile) {
     it.n_rows = min(AT_BM, seg_end - it.row0);
     it.pos0 = p.seg_pos[seg] + (it.row0 - seg_begin);            // position of the first row
     it.k_hi_all = it.pos0 + it.n_rows - 1;
-    it.k_lo_all = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    it.k_lo_all = kp_key_lo(it.pos0, p.window, p.block);
     it.kt_lo = it.k_lo_all / AT_BN;
     it.kt_hi = it.k_hi_all / AT_BN;
     it.bt = p.block_table + (size_t)seg * p.max_blocks;
@@ -217,8 +218,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             const AtItem it = at_item(p, item_tile(idx));
             const int pos = it.pos0 + r;                                  // this row's position (rows >= n_rows: masked)
             const bool live = r < it.n_rows;
-            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-            const int lo_max = p.window > 0 ? max(0, it.k_hi_all - p.window + 1) : 0;    // the last row's first key
+            const int lo = kp_key_lo(pos, p.window, p.block);
+            const int lo_max = kp_key_lo(it.k_hi_all, p.window, p.block);    // the last row's first key
             float o[AT_HD];
 #pragma unroll
             for (int d = 0; d < AT_HD; d++) o[d] = 0.f;
@@ -489,8 +490,8 @@ attn_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             const AtItem it = at_item(p, item_tile(idx));
             const int pos = it.pos0 + r;
             const bool live = r < it.n_rows;
-            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-            const int lo_max = p.window > 0 ? max(0, it.k_hi_all - p.window + 1) : 0;
+            const int lo = kp_key_lo(pos, p.window, p.block);
+            const int lo_max = kp_key_lo(it.k_hi_all, p.window, p.block);
             float m = -INFINITY, l = 0.f;
             for (int kt = it.kt_lo; kt <= it.kt_hi; kt++, i++) {
                 if (ok && (*abort_flag || !kp_mbar_wait_bounded(&s_full[g], i & 1))) ok = false;
@@ -612,11 +613,13 @@ extern "C" {
 
 // tile_seg / tile_row0: the 128-row tiles of the step, most keys first (device arrays, n_tiles long);
 // n_rows_total: rows of q.
-int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void* cache, long long n_pages,
-                            const int* block_table, int max_blocks, const int* cu_rows, const int* seg_pos,
-                            const int* tile_seg, const int* tile_row0, int n_tiles, void* out, int ldo, float scale,
-                            int window, int page_size, int H, int G, int hd, void* stream) {
+// block: 0, or the size of the blocks of positions beyond whose start a row reads no key.
+int kp_attention_prefill_tc_masked(const void* q, int ldq, int n_rows_total, const void* cache, long long n_pages,
+                                   const int* block_table, int max_blocks, const int* cu_rows, const int* seg_pos,
+                                   const int* tile_seg, const int* tile_row0, int n_tiles, void* out, int ldo, float scale,
+                                   int window, int block, int page_size, int H, int G, int hd, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (block < 0) return KP_ERR_BAD_ARG;
     if (hd != AT_HD || G < 1 || H % G || H > 65535 || (ldq & 7) || (ldo & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
         ((uintptr_t)cache & 15) || page_size < 8 || (page_size % 8) || !(page_size % AT_BN == 0 || AT_BN % page_size == 0) ||
         n_pages <= 0 || n_pages * 2 * G * page_size >= 2147483647LL)
@@ -630,6 +633,7 @@ int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void
     AtArgs a = {};
     a.block_table = block_table; a.max_blocks = max_blocks; a.cu_rows = cu_rows; a.seg_pos = seg_pos;
     a.tile_seg = tile_seg; a.tile_row0 = tile_row0; a.out = (bf16*)out; a.ldo = ldo; a.scale = scale; a.window = window;
+    a.block = block;
     a.page_size = page_size; a.H = H; a.G = G; a.n_tiles = n_tiles;
     if (g_at_pair && (H / G) % 2 == 0) {
         const size_t smem2 = 1024 + 10 * AT_TILE_BYTES + 17 * 8 + 16;
@@ -651,6 +655,14 @@ int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void
     }
     kp_launch_pdl(attn_prefill_tc_kernel, dim3((n_tiles + 1) / 2, H), dim3(AT_THREADS), smem, (cudaStream_t)stream, tq, tc, a);
     return kp_launch_status();
+}
+
+int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void* cache, long long n_pages,
+                            const int* block_table, int max_blocks, const int* cu_rows, const int* seg_pos,
+                            const int* tile_seg, const int* tile_row0, int n_tiles, void* out, int ldo, float scale,
+                            int window, int page_size, int H, int G, int hd, void* stream) {
+    return kp_attention_prefill_tc_masked(q, ldq, n_rows_total, cache, n_pages, block_table, max_blocks, cu_rows, seg_pos,
+                                          tile_seg, tile_row0, n_tiles, out, ldo, scale, window, 0, page_size, H, G, hd, stream);
 }
 
 // 1 (default): two heads a CTA where the head counts allow it; 0: one head a CTA always.  For measurements and tests.

@@ -52,6 +52,15 @@ __device__ __forceinline__ float kp_act_silu_or_relu(int act, float g) {
 #define KP_EPI_ACT(epi) (((epi) >> 8) & 0xff)
 #define KP_EPI_KIND(epi) ((epi) & 0xff)
 
+// The first key a row at position `pos` may read: `window` > 0 keeps the last `window` keys, `block` > 0 lets
+// it read no key from before the start of its own block of `block` positions (blocks counted from position 0 of
+// the sequence).  Non-decreasing in pos.
+__device__ __forceinline__ int kp_key_lo(int pos, int window, int block) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (block > 0) lo = max(lo, (pos / block) * block);
+    return lo;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -546,16 +546,16 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
         raise KernelError("attention_split: scratch too small")
     lib = load_library("attention_decode")
-    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0 and not block:
+    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
         # tensor-core chunk pass over smaller chunks, then the same merge
         parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
-        _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma, 
+        _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma_masked,
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
-            _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), page_size,
-            n, H, G, hd, STREAM)
-        _run("attention_merge", lib.kp_attention_merge, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
-                                      SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), STREAM)
+            _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), int(block or 0),
+            page_size, n, H, G, hd, STREAM)
+        _run("attention_merge", lib.kp_attention_merge_masked, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
+             parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
     _run("attention_split", lib.kp_attention_split_masked, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table),
          block_table.shape[1], _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
@@ -589,12 +589,13 @@ def attention_prefill_ok(q: torch.Tensor, hd: int) -> bool:
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, cu_rows: torch.Tensor,
                       seg_pos: torch.Tensor, tile_seg: torch.Tensor, tile_row0: torch.Tensor, out: torch.Tensor,
                       scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int,
-                      big_tile_seg: Optional[torch.Tensor] = None, big_tile_row0: Optional[torch.Tensor] = None
-                      ) -> torch.Tensor:
+                      big_tile_seg: Optional[torch.Tensor] = None, big_tile_row0: Optional[torch.Tensor] = None,
+                      block: Optional[int] = None) -> torch.Tensor:
     """Tensor-core causal attention for segments of many rows.  ``tile_seg`` / ``tile_row0`` list, for every
     tile of 64 consecutive rows of a segment, its segment and its first row; ``big_tile_seg`` /
     ``big_tile_row0`` the same for tiles of 128 rows, the tile that reads the most keys first (with them the
-    tcgen05 kernel runs where it takes the sizes)."""
+    tcgen05 kernel runs where it takes the sizes).  ``block``: a row reads no key from before the start of its own
+    block of that many positions."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(cache, "cache", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
     for t_, nm in ((block_table, "block_table"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (tile_seg, "tile_seg"),
@@ -609,16 +610,17 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         _need(big_tile_seg, "big_tile_seg", torch.int32); _need(big_tile_row0, "big_tile_row0", torch.int32)
         if big_tile_seg.numel() != big_tile_row0.numel():
             raise KernelError("attention_prefill: tile lists differ in length")
-        _run("attention_prefill_tc", load_library("attention_tc").kp_attention_prefill_tc, 
+        _run("attention_prefill_tc", load_library("attention_tc").kp_attention_prefill_tc_masked,
             _ptr(q), _rows_2d(q, "q"), n, _ptr(cache), ctypes.c_longlong(cache.shape[0]), _ptr(block_table),
             block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos), _ptr(big_tile_seg), _ptr(big_tile_row0),
             big_tile_seg.numel(),
-            _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), page_size, H, G, hd, STREAM)
+            _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), int(block or 0), page_size, H, G, hd,
+            STREAM)
         return out
-    _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma, 
+    _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma_masked,
         _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
         _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
-        int(window or 0), page_size, H, G, hd, STREAM)
+        int(window or 0), int(block or 0), page_size, H, G, hd, STREAM)
     return out
 
 

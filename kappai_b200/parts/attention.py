@@ -193,13 +193,12 @@ class Attention(Part):
                               view.page_size, H, G, hd)
         o = torch.empty_like(q)
         tiles = ctx.tables.get(self.step_tables_key)
-        tiled_ok = self.block is None            # the tiled prompt kernels know windows, not blocks of positions
         if self.split_ok and (tiles is None or q.dtype == torch.float32):
             # rows that each read a long cache (decode): split the keys over many CTAs.  The 32-bit path
             # takes this kernel for every row, whatever the length of its segment: its chunks lie at absolute
             # multiples of 256 keys and are summed in order, so a row's bits do not depend on how the step was cut.
             self._split(q, o, ctx, view, cache, ctx.n_rows)
-        elif tiles is not None and tiled_ok and K.attention_prefill_ok(q, hd):
+        elif tiles is not None and K.attention_prefill_ok(q, hd):
             lead = tiles.n_short_rows
             if lead and self.split_ok:
                 # decoded tokens beside prompt portions: the decoded rows lead the batch and go to the split
@@ -208,12 +207,13 @@ class Attention(Part):
                 t0 = tiles.n_short_tiles
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg[t0:],
                                     tiles.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
-                                    tiles.big_tile_seg, tiles.big_tile_row0)
+                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block)
             else:
                 # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
                 big = (None, None) if lead else (tiles.big_tile_seg, tiles.big_tile_row0)
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
-                                    tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big)
+                                    tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big,
+                                    block=self.block)
         else:
             lead = tiles.n_short_rows if tiles is not None else 0
             if lead and self.split_ok:

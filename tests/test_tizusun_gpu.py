@@ -180,6 +180,62 @@ def test_a_key_just_inside_and_just_outside_the_block(H, G, hd, block, page, ker
     assert np.abs(got - want).max() < (2e-5 if dt == torch.float32 else 2e-2), (kernel, np.abs(got - want).max())
 
 
+@pytest.mark.parametrize("variant", ["tcgen05 two heads a CTA", "tcgen05 one head a CTA", "mma.sync"])
+@pytest.mark.parametrize("H,G,hd,page,block", [(4, 2, 64, 64, 100), (6, 1, 64, 16, 24), (2, 2, 128, 32, 130), (8, 2, 64, 64, 512),
+                                               (2, 1, 64, 64, 128)])
+def test_tiled_prompt_kernels_keep_to_the_block(H, G, hd, page, block, variant):
+    """Prompt portions (from position 0, from the middle of a block, from a block's first position, single rows)
+    through the tensor-core kernels with a block mask, against the plain masked softmax.  In every sequence the
+    block's first key and the key before it are made to stand out for some rows."""
+    from kappai_b200.ops import kernels as Kn
+    from kappai_b200.ops.build import load_library
+    from test_kernels_gpu import dev as dv, i32, paged_setup, rt
+    DT = torch.bfloat16
+    rng = np.random.default_rng(block)
+    seq_lens = [3 * block + 17, 2 * block, block + 1, 700, 64]
+    q_from = [0, block + block // 2, block, 650, 63]
+    cache, bt, ks, vs = paged_setup(rng, seq_lens, page, G, hd, DT)
+    qs = [rt(rng.standard_normal((L, H, hd)), DT) for L in seq_lens]
+    for i, L in enumerate(seq_lens):
+        for p in range(q_from[i], L, 5):
+            b0 = p // block * block
+            target = b0 if (p // 5) % 2 == 0 else b0 - 1                    # just inside / just outside
+            if target >= 0:
+                g = (p // 5) % G
+                qs[i][p, g * (H // G):(g + 1) * (H // G)] = rt(ks[i][target, g] * 3.0, DT)
+    old = Kn.USE_TC_ATTENTION
+    Kn.USE_TC_ATTENTION = variant != "mma.sync"
+    load_library("attention_tc").kp_attention_tc_set_pair(1 if "two heads" in variant else 0)
+    try:
+        rows, cu, seg_pos, tile_seg, tile_row0, big = [], [0], [], [], [], []
+        for i, (L, a) in enumerate(zip(seq_lens, q_from)):
+            rows.append(qs[i][a:])
+            for r0 in range(cu[-1], cu[-1] + L - a, Kn.PREFILL_TILE):
+                tile_seg.append(i); tile_row0.append(r0)
+            for r0 in range(cu[-1], cu[-1] + L - a, 128):
+                big.append((-(a + min(r0 + 128, cu[-1] + L - a) - cu[-1] - 1), i, r0))
+            cu.append(cu[-1] + L - a)
+            seg_pos.append(a)
+        big.sort()
+        q_rows = np.concatenate(rows, 0).reshape(cu[-1], H * hd)
+        out = torch.empty((cu[-1], H * hd), dtype=DT, device=DEV)
+        scale = 1.0 / math.sqrt(hd)
+        Kn.attention_prefill(dv(q_rows, DT), dv(cache, DT), i32(bt), i32(cu), i32(seg_pos), i32(tile_seg), i32(tile_row0), out,
+                             scale, None, page, H, G, hd, i32([x[1] for x in big]), i32([x[2] for x in big]), block=block)
+        got = out.cpu().double().numpy().reshape(cu[-1], H, hd)
+        assert Kn.attention_tc_status() == 0 and Kn.attention_mma_status() == 0
+    finally:
+        Kn.USE_TC_ATTENTION = old
+        load_library("attention_tc").kp_attention_tc_set_pair(1)
+    for i, (L, a) in enumerate(zip(seq_lens, q_from)):
+        vis = P.block_causal_mask(np.arange(L), block)[a:]
+        for h in range(H):
+            g = h // (H // G)
+            w = P.masked_softmax((qs[i][a:, h] @ ks[i][:, g].T) * scale, vis)
+            err = np.abs(got[cu[i]:cu[i + 1], h] - w @ vs[i][:, g]).max()
+            assert err <= 2e-2, (variant, i, h, err)
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 16), (5, 6, 1, 64, 24), (70, 3, 2, 48, 40), (33, 8, 8, 40, 12),
                                           (200, 16, 3, 128, 64), (9, 5, 2, 36, 10)])
