@@ -31,6 +31,12 @@ shape, 256 requests at once, prompts of 16 to 512 tokens, 128 sampled tokens
 each at temperature 0.8) run whole generations through ``Engine`` and print a
 line of their own: tokens a second, steps, preemptions, mean step time.
 
+``--design tizusun`` times the Tizusun design (post-norm layers, attention with a block mask, a gate and
+key-projection values, dense and mixture-of-experts feed-forwards) at a few layer sizes of real models, with
+random weights, beside an LFM2 model of attention layers of the same sizes: one 2,048-token prompt in one step
+and decode steps of ``--batch`` requests at a context of about 2,048, on the device, and the device time of
+both steps by kernel class.  It prints a line of its own; the default line is unchanged.
+
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and
 exits with 2.
 """
@@ -382,6 +388,116 @@ def run_workload(name: str, rng_seed: int, time_kernels: bool = False) -> dict:
     return rec
 
 
+# ------------------------------------------------------------------------------------- --design tizusun
+# (name, width, heads, kv heads, head size, dense ff, experts, top, expert ff, layers: d = dense, m = mixture)
+DESIGN_SIZES = [
+    ("1024x16h64", 1024, 16, 8, 64, 2816, 8, 4, 704, "dmmm"),
+    ("2048x32h64", 2048, 32, 8, 64, 5632, 16, 4, 1408, "dmmm"),
+    ("4096x32h128", 4096, 32, 8, 128, 11264, 32, 8, 1408, "dm"),
+]
+DESIGN_VOCAB = 65536
+DESIGN_BLOCK = 8192
+
+
+def tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers):
+    mixer = {"dim": hd, "vdim": hd, "heads": H, "kv_heads": G, "scale": hd ** -0.5, "mask": {"size": DESIGN_BLOCK},
+             "rot": {"base": 500000.0, "dims": hd // 2,
+                     "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff_e}, "router": {"experts": E, "top": top}}
+    return {"architecture": "Tizusun", "vocab": DESIGN_VOCAB, "width": width, "postln_alpha": 2.0, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": dict(dense if c == "d" else moe)} for c in layers]}
+
+
+def lfm2_like_config(width, H, G, hd, ff, n_layers):
+    return dict(architectures=["Lfm2ForCausalLM"], vocab_size=DESIGN_VOCAB, hidden_size=width, num_hidden_layers=n_layers,
+                num_attention_heads=H, num_key_value_heads=G, head_dim=hd, layer_types=["full_attention"] * n_layers,
+                max_position_embeddings=131072, norm_eps=1e-5, conv_L_cache=3, conv_bias=False, block_ff_dim=ff,
+                block_auto_adjust_ff_dim=False, rope_theta=1000000.0, tie_embedding=False)
+
+
+def folder_for(cfg, seed):
+    from kappai_b200.weights import write_random_model
+
+    key = hashlib.sha256(json.dumps([cfg, seed], sort_keys=True).encode()).hexdigest()[:12]
+    d = os.path.join(tempfile.gettempdir(), f"kappai_b200_bench_{os.getuid()}_{key}")
+    if not os.path.isfile(os.path.join(d, ".complete")):
+        print(f"[bench] writing random weights to {d} ...", file=sys.stderr, flush=True)
+        write_random_model(cfg, d, seed)
+        with open(os.path.join(d, ".complete"), "w") as f:
+            f.write("ok")
+    return d
+
+
+def kernel_classes(runner, entries_fn, n):
+    """Device time by kernel class of ``n`` eager steps (every launch between two CUDA events)."""
+    import torch
+    from kappai_b200.ops import kernels as K
+
+    timer = K.KernelTimer()
+    K.TIMER[0] = timer
+    try:
+        for _ in range(n):
+            entries_fn()
+        torch.cuda.synchronize()
+    finally:
+        K.TIMER[0] = None
+    return [{"class": key, "us": round(per, 2), "calls": calls // n, "share": round(share, 1),
+             "tflops": None if tf is None else round(tf, 1), "gbs": None if gb is None else round(gb, 1)}
+            for key, calls, ms, per, share, tf, gb in timer.report()]
+
+
+def run_design(a) -> int:
+    import numpy as np
+    import torch
+    from kappai_b200 import ModelRunner, StepEntry
+
+    pk = peaks()
+    T, B, ctx_len = PROMPT_LEN, a.batch, PROMPT_LEN + 256
+    warmup = max(a.warmup, 3)
+    steps = min(a.steps, 128)
+    out = {"design": "Tizusun", "beside": "LFM2 attention layers of the same sizes", "dtype": "bf16",
+           "data": "synthetic: random weights, uniform random token ids", "prompt_tokens": T, "decode_batch": B,
+           "decode_context": f"{T} to {ctx_len}", "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, width, H, G, hd, ff, E, top, ff_e, layers in DESIGN_SIZES:
+        if a.size and a.size != name:
+            continue
+        rec = {}
+        for model, cfg in (("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers)),
+                           ("lfm2", lfm2_like_config(width, H, G, hd, ff, len(layers)))):
+            rng = np.random.default_rng(SEED)
+            runner = ModelRunner(folder_for(cfg, SEED), dtype="bfloat16", max_tokens=(B + 1) * (ctx_len + 64), max_requests=B + 1,
+                                 page_size=64, max_model_len=ctx_len + 64)
+            pf_ms, pf_all = run_prefill(runner, T, warmup, rng)
+            win, _ = run_decode(runner, B, T, ctx_len, steps, warmup, rng)
+            V = runner.vocab_size
+            toks = rng.integers(0, V, T).tolist()
+
+            def prefill_step():
+                runner.step([StepEntry("p", toks, [T - 1])])
+                runner.end("p")
+
+            pf_classes = kernel_classes(runner, prefill_step, 3)
+            ids = list(range(B))
+            for i in ids:
+                runner.step([StepEntry(i, rng.integers(0, V, T).tolist(), [])])
+            dec_classes = kernel_classes(runner, lambda: runner.step([StepEntry(i, [1], [0]) for i in ids]), 8)
+            for i in ids:
+                runner.end(i)
+            rec[model] = {"layers": len(layers), "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(T * 1e3 / pf_ms, 1),
+                          "decode_ms_per_step": round(win["mid"][0], 4), "decode_tok_s": round(B * 1e3 / win["mid"][0], 1),
+                          "weight_gb": round(weight_bytes(runner) / 1e9, 3),
+                          "prefill_kernels": pf_classes, "decode_kernels": dec_classes}
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = rec
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def run_probe(model_dir, a, rng) -> int:
     """A few eager steps for a profiler: every kernel is a launch of its own (no graph), sizes as in the bench."""
     import torch
@@ -493,6 +609,10 @@ def main() -> int:
                     help="with --workload: launch every kernel on its own between CUDA events and print the device "
                          "time by kernel class (the run's throughput is then not the engine's)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
+    ap.add_argument("--design", choices=["tizusun"], default=None,
+                    help="time another design at a few layer sizes beside LFM2 attention layers of the same sizes "
+                         "(prefill, decode, device time by kernel class) instead of the default line")
+    ap.add_argument("--size", default=None, help="with --design: one of its sizes only (e.g. 2048x32h64)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -508,6 +628,8 @@ def main() -> int:
     if a.workload:
         print(json.dumps(run_workload(a.workload, 40, a.time)))
         return 0
+    if a.design:
+        return run_design(a)
 
     import numpy as np
     import torch

@@ -16,9 +16,10 @@
 //   moe_combine: out[r] += sum over j of weight_j * y[place of (r, j)], j ascending.
 // The products exist in two forms: CUDA-core float32 FMA (the true 32-bit path, and every shape), and
 // bfloat16 tensor-core tiles (mma.sync m16n8k16, float32 accumulation) for 16-bit storage.
-#include "common.cuh"
+#include "tcgen05.cuh"
 
-#define MOE_BM 32                // rows of a tile
+#define MOE_BM 32                // rows of a tile of the mma.sync and CUDA-core products
+#define MOE_BIG 128              // rows of a tile of the tcgen05 products
 #define MOE_MAX_TOP 32
 #define MOE_SORT_THREADS 1024
 
@@ -63,12 +64,84 @@ moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* _
     }
 }
 
+// The router as one kernel: logits z = h Wr^T + b in float32 (h is widened from its storage type; a row's
+// logit sums k in an order fixed by the lane pattern, whatever the batch), then the choice as above.  A block
+// takes MOE_RB rows, which stay in shared memory as float32 while each warp walks its experts' rows of Wr.
+#define MOE_RB 4
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr, const float* __restrict__ bias, int n,
+                  int E, int d, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
+    kp_pdl_begin();
+    extern __shared__ __align__(16) float router_sm[];          // [MOE_RB][d] rows, [MOE_RB][E] logits
+    float* hs = router_sm;
+    float* zs = router_sm + (size_t)MOE_RB * d;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.x * MOE_RB, nr = min(MOE_RB, n - row0);
+    for (int i = threadIdx.x; i < MOE_RB * d; i += blockDim.x) {
+        const int r = i / d, k = i - r * d;
+        hs[i] = r < nr ? to_f32(h[(size_t)(row0 + r) * ldh + k]) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const float4* w4 = reinterpret_cast<const float4*>(wr + (size_t)e * d);
+        float acc[MOE_RB];
+#pragma unroll
+        for (int r = 0; r < MOE_RB; r++) acc[r] = 0.f;
+        for (int k = lane * 4; k < d; k += 128) {
+            const float4 w = __ldg(w4 + (k >> 2));
+#pragma unroll
+            for (int r = 0; r < MOE_RB; r++) {
+                const float4 x = *reinterpret_cast<const float4*>(hs + (size_t)r * d + k);
+                acc[r] = fmaf(x.x, w.x, acc[r]); acc[r] = fmaf(x.y, w.y, acc[r]);
+                acc[r] = fmaf(x.z, w.z, acc[r]); acc[r] = fmaf(x.w, w.w, acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MOE_RB; r++) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0) zs[(size_t)r * E + e] = v + (bias ? bias[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    if (warp >= nr) return;
+    float* z = zs + (size_t)warp * E;                            // warp r chooses for row r
+    float my_z = -INFINITY;
+    int my_e = 0;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;
+        if (lane == j) { my_z = best; my_e = bi; }
+        if (lane == 0) z[bi] = -INFINITY;
+        __syncwarp();
+    }
+    const float m = __shfl_sync(0xffffffffu, my_z, 0);
+    const float p = lane < top ? expf(my_z - m) : 0.f;
+    const float sum = warp_sum(p);
+    if (lane < top) {
+        idx_out[(size_t)(row0 + warp) * top + lane] = my_e;
+        w_out[(size_t)(row0 + warp) * top + lane] = p / sum;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------- sort
 // offsets[e] .. offsets[e+1]: the places of expert e's pairs; tile_start[e] .. tile_start[e+1]: its row tiles
-// of MOE_BM places (tile_start[E] = all tiles).  perm[place] = pair (row * top + j); inv[pair] = place.
+// of MOE_BM places (tile_start[E] = all tiles), big_start the same for tiles of MOE_BIG places.
+// perm[place] = pair (row * top + j); inv[pair] = place.
 __global__ void __launch_bounds__(MOE_SORT_THREADS)
 moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ offsets, int* __restrict__ tile_start,
-                int* __restrict__ perm, int* __restrict__ inv) {
+                int* __restrict__ big_start, int* __restrict__ perm, int* __restrict__ inv) {
     kp_pdl_begin();
     extern __shared__ int sort_sm[];                            // [E] counts, [E] cursors, [E + 1] offsets
     int* cnt = sort_sm;
@@ -79,13 +152,14 @@ moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
-        int o = 0, t = 0;
+        int o = 0, t = 0, tb = 0;
         for (int e = 0; e < E; e++) {
-            off[e] = o; offsets[e] = o; tile_start[e] = t;
+            off[e] = o; offsets[e] = o; tile_start[e] = t; big_start[e] = tb;
             o += cnt[e];
             t += (cnt[e] + MOE_BM - 1) / MOE_BM;
+            tb += (cnt[e] + MOE_BIG - 1) / MOE_BIG;
         }
-        off[E] = o; offsets[E] = o; tile_start[E] = t;
+        off[E] = o; offsets[E] = o; tile_start[E] = t; big_start[E] = tb;
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
@@ -98,7 +172,7 @@ moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict
 
 // The expert and the rows of row tile `bt` (false: no such tile in this step).
 __device__ __forceinline__ bool moe_tile(const int* __restrict__ offsets, const int* __restrict__ tile_start, int E, int bt,
-                                         int& e, int& row0, int& row1) {
+                                         int& e, int& row0, int& row1, int rows_a_tile = MOE_BM) {
     if (bt >= tile_start[E]) return false;
     int lo = 0, hi = E;                                         // the last e with tile_start[e] <= bt
     while (hi - lo > 1) {
@@ -106,8 +180,8 @@ __device__ __forceinline__ bool moe_tile(const int* __restrict__ offsets, const 
         if (tile_start[mid] <= bt) lo = mid; else hi = mid;
     }
     e = lo;
-    row0 = offsets[e] + (bt - tile_start[e]) * MOE_BM;
-    row1 = min(row0 + MOE_BM, offsets[e + 1]);
+    row0 = offsets[e] + (bt - tile_start[e]) * rows_a_tile;
+    row1 = min(row0 + rows_a_tile, offsets[e + 1]);
     return true;
 }
 
@@ -352,6 +426,190 @@ moe_down_tc_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w_down
             }
 }
 
+// --------------------------------------------------------------------- products on tcgen05 (many rows)
+// The grouped products of a prompt portion on the 5th-generation tensor cores.  A CTA computes one tile:
+// MOE_BIG places of one expert by 128 accumulator columns.  Warp 0 is the TMA producer (k-blocks of 64 through a
+// ring of MT_STAGES stages: a box of 128 rows of the left operand, which lies place by place, and the expert's
+// rows of W, both with the 128-byte swizzle), one lane of warp 1 issues the tcgen05.mma (128 x 128 x 16, the
+// accumulator in tensor memory), warps 2 to 5 read the accumulator with tcgen05.ld, each its quarter of the
+// lanes, and write the rows that belong to the expert (a box may reach into the next expert's places; what the
+// MMA makes of those rows is not stored).  Gated form: the W tile is 64 gate rows and the matching 64 up rows,
+// accumulator columns c and 64 + c are gate and up of output column c, and the epilogue writes
+// act(gate) * up in bfloat16.  Plain form: 128 output columns in float32.  Two CTAs fit an SM, so one's
+// epilogue runs under the other's main loop.  Every wait is bounded; one that gives up sets the status word.
+KP_STATUS_WORD(g_moe_tc_status, moe_tc)
+
+#define MT_BN 128
+#define MT_BK 64
+#define MT_STAGES 3
+#define MT_THREADS 192
+#define MT_A_BYTES (MOE_BIG * MT_BK * 2)
+#define MT_B_BYTES (MT_BN * MT_BK * 2)
+
+struct MtArgs {
+    const int* offsets; const int* big_start;
+    int E, K;
+    int n_out;                 // output columns: ff (gated) or d
+    int w_rows;                // rows of W an expert has: 2 ff (gated) or d
+    int up_off;                // gated: the up rows lie this many rows behind the gate rows (ff)
+    void* out; int ldo;
+    int act;
+};
+
+template <bool GATED>
+__global__ void __launch_bounds__(MT_THREADS)
+moe_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const MtArgs p) {
+    constexpr int N_TILE = GATED ? MT_BN / 2 : MT_BN;
+    extern __shared__ unsigned char mt_smem[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)mt_smem + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)MT_STAGES * (MT_A_BYTES + MT_B_BYTES));
+    uint64_t* empty = full + MT_STAGES;
+    uint64_t* acc_full = empty + MT_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmW)) : "memory");
+        for (int s = 0; s < MT_STAGES; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], 1); }
+        kp_mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        kp_mbar_init_fence();
+    }
+    if (warp == 1) kp_tmem_alloc(tmem_slot, MT_BN);
+    kp_tc_fence_before();
+    __syncthreads();
+    kp_tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    kp_pdl_begin();                                  // the layout and the operands come from the kernels before
+
+    int e = 0, row0 = 0, row1 = 0;
+    const bool live = moe_tile(p.offsets, p.big_start, p.E, blockIdx.y, e, row0, row1, MOE_BIG);
+    const int n0 = blockIdx.x * N_TILE;
+    const int n_kb = (p.K + MT_BK - 1) / MT_BK;
+    if (live && warp == 0) {
+        if (lane == 0) {
+            const int w0 = e * p.w_rows + n0;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (*abort_flag || !kp_mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; break; }
+                unsigned char* a_dst = tiles + (size_t)s * (MT_A_BYTES + MT_B_BYTES);
+                kp_mbar_expect_tx(&full[s], MT_A_BYTES + MT_B_BYTES);
+                kp_tma_load_2d(a_dst, &tmA, kb * MT_BK, row0, &full[s]);
+                if (GATED) {
+                    kp_tma_load_2d(a_dst + MT_A_BYTES, &tmW, kb * MT_BK, w0, &full[s]);
+                    kp_tma_load_2d(a_dst + MT_A_BYTES + MT_B_BYTES / 2, &tmW, kb * MT_BK, w0 + p.up_off, &full[s]);
+                } else {
+                    kp_tma_load_2d(a_dst + MT_A_BYTES, &tmW, kb * MT_BK, w0, &full[s]);
+                }
+                if (++s == MT_STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+    } else if (live && warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = kp_umma_idesc(MOE_BIG, MT_BN);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (*abort_flag || !kp_mbar_wait_bounded(&full[s], ph)) { *abort_flag = 1; ok = false; break; }
+                kp_tc_fence_after();
+                const uint32_t a_addr = kp_smem_u32(tiles + (size_t)s * (MT_A_BYTES + MT_B_BYTES));
+                const uint64_t adesc = kp_umma_desc(a_addr), bdesc = kp_umma_desc(a_addr + MT_A_BYTES);
+#pragma unroll
+                for (int k = 0; k < MT_BK / 16; k++) kp_umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                kp_umma_commit(&empty[s]);
+                if (++s == MT_STAGES) { s = 0; ph ^= 1; }
+            }
+            if (ok) kp_umma_commit(acc_full);
+        }
+    } else if (live) {
+        const int q = warp & 3;                              // the quarter of the lanes this warp may read
+        const bool ok = kp_mbar_wait_bounded(acc_full, 0) && !*abort_flag;
+        if (!ok) *abort_flag = 1;
+        kp_tc_fence_after();
+        const int m = row0 + q * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (ok) {
+            if (GATED) {
+                bf16* dst = (bf16*)p.out + (size_t)m * p.ldo;
+                const bool vec = (p.ldo & 7) == 0 && (((uintptr_t)p.out) & 15) == 0;
+#pragma unroll 1
+                for (int c = 0; c < N_TILE; c += 32) {
+                    uint32_t g[32], u[32];
+                    kp_tmem_ld32_issue(lane_base + c, g);
+                    kp_tmem_ld32_issue(lane_base + N_TILE + c, u);
+                    kp_tmem_ld_wait();
+                    if (m < row1) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float gq = to_f32(from_f32<bf16>(__uint_as_float(g[j]))), uq = to_f32(from_f32<bf16>(__uint_as_float(u[j])));
+                            v[j] = kp_act_rt(p.act, gq) * uq;
+                        }
+                        if (vec && n0 + c + 32 <= p.n_out) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 o;
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]), t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+                                o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+                                *reinterpret_cast<uint4*>(dst + n0 + c + j) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (n0 + c + j < p.n_out) dst[n0 + c + j] = from_f32<bf16>(v[j]);
+                        }
+                    }
+                }
+            } else {
+                float* dst = (float*)p.out + (size_t)m * p.ldo;
+                const bool vec = (p.ldo & 3) == 0 && (((uintptr_t)p.out) & 15) == 0;
+#pragma unroll 1
+                for (int c = 0; c < N_TILE; c += 32) {
+                    uint32_t r[32];
+                    kp_tmem_ld32(lane_base + c, r);
+                    if (m < row1) {
+                        if (vec && n0 + c + 32 <= p.n_out) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + n0 + c + j) =
+                                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (n0 + c + j < p.n_out) dst[n0 + c + j] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    kp_tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(&g_moe_tc_status, 1);
+        kp_linger_after_failure();
+    }
+    if (warp == 1) kp_tmem_dealloc(tmem_base, MT_BN);
+}
+
+// hs[place, :] = h[row of the pair at that place, :]   (16 bytes a thread and turn)
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, int ldh, const int* __restrict__ perm, bf16* __restrict__ hs,
+                                       int n_pairs, int d8, int top) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n_pairs * d8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t place = i / d8, c = (i % d8) * 8;
+        *reinterpret_cast<uint4*>(hs + place * (size_t)d8 * 8 + c) =
+            *reinterpret_cast<const uint4*>(h + (size_t)(perm[place] / top) * ldh + c);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- combine
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ w,
                                    float* __restrict__ out, int n, int d, int top) {
@@ -365,10 +623,15 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
+static long long g_moe_tc_min_pairs = 512;      // (row, choice) pairs from which the tcgen05 tiles are taken
+
 extern "C" {
 
-// Ints of scratch for the layout of one step: offsets [E + 1], tile_start [E + 1], perm [n top], inv [n top].
-long long kp_moe_layout_ints(int n, int E, int top) { return 2LL * (E + 1) + 2LL * n * top; }
+// For measurements and tests: the number of pairs from which the tcgen05 path runs.
+void kp_moe_set_tc_min_pairs(long long v) { g_moe_tc_min_pairs = v; }
+
+// Ints of scratch for the layout of one step: offsets, tile_start, big_start [E + 1 each], perm [n top], inv [n top].
+long long kp_moe_layout_ints(int n, int E, int top) { return 3LL * (E + 1) + 2LL * n * top; }
 
 // Row tiles a step of n rows can have at most (a grid axis of the grouped products).
 int kp_moe_max_tiles(int n, int E, int top) {
@@ -388,16 +651,48 @@ int kp_moe_route(const float* logits, int n, int E, int top, int* idx, float* we
     if (e0 != cudaSuccess) return (int)e0;
     int* offsets = layout;
     int* tile_start = offsets + (E + 1);
-    int* perm = tile_start + (E + 1);
+    int* big_start = tile_start + (E + 1);
+    int* perm = big_start + (E + 1);
     int* inv = perm + (size_t)n * top;
     kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, offsets, tile_start,
-                  perm, inv);
+                  big_start, perm, inv);
+    return kp_launch_status();
+}
+
+// The router in one go: rows h [n, d] (storage type `dtype`), Wr [E, d] and b [E] (or null) in float32 -> idx, weights
+// and the layout.  KP_ERR_UNSUPPORTED where the rows do not fit the kernel's shared memory or alignment (the caller
+// then computes the logits with a matrix product and calls kp_moe_route).
+int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, int n, int E, int d, int top, int* idx,
+                  float* weights, int* layout, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return KP_ERR_UNSUPPORTED;
+    const size_t sm = ((size_t)MOE_RB * d + (size_t)MOE_RB * E) * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
+    if ((d & 3) || ((uintptr_t)wr & 15) || sm > 200 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    KP_DISPATCH_DTYPE(dtype, T, {
+        if (sm > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            if (e != cudaSuccess) return (int)e;
+        }
+        kp_launch_pdl(moe_router_kernel<T>, dim3((n + MOE_RB - 1) / MOE_RB), dim3(256), sm, s, (const T*)h, ldh, wr, bias, n, E, d,
+                      top, idx, weights);
+    });
+    cudaError_t e0 = cudaGetLastError();
+    if (e0 != cudaSuccess) return (int)e0;
+    int* offsets = layout;
+    int* tile_start = offsets + (E + 1);
+    int* big_start = tile_start + (E + 1);
+    int* perm = big_start + (E + 1);
+    int* inv = perm + (size_t)n * top;
+    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, offsets, tile_start,
+                  big_start, perm, inv);
     return kp_launch_status();
 }
 
 // h [n, d] -> act [n top, ff] (by place) -> y [n top, d] float32 (by place) -> out [n, d] += weighted sum.
+// hs: scratch [n top, d] in the storage type for the tcgen05 path (null: that path is not taken).
 int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
-                   void* act, float* y, float* out, int n, int E, int top, int d, int ff, int act_kind, int dtype,
+                   void* act, float* y, float* out, void* hs, int n, int E, int top, int d, int ff, int act_kind, int dtype,
                    void* stream) {
     if (n <= 0) return 0;
     if (E < 1 || top < 1 || d < 1 || ff < 1 || act_kind < 0 || act_kind > KP_ACT_GELU_TANH) return KP_ERR_BAD_ARG;
@@ -406,12 +701,43 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
     cudaStream_t s = (cudaStream_t)stream;
     const int* offsets = layout;
     const int* tile_start = offsets + (E + 1);
-    const int* perm = tile_start + (E + 1);
+    const int* big_start = tile_start + (E + 1);
+    const int* perm = big_start + (E + 1);
     const int* inv = perm + (size_t)n * top;
     cudaError_t e0;
     const bool tc = dtype == KP_DTYPE_BF16 && d % 8 == 0 && ff % 8 == 0 && ldh % 8 == 0 &&
                     !(((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) & 15);
-    if (tc) {
+    const long long pairs = (long long)n * top;
+    const long long big_tiles = pairs / MOE_BIG + (pairs < E ? pairs : E);
+    if (tc && hs != nullptr && pairs >= g_moe_tc_min_pairs && big_tiles <= 65535 && !((uintptr_t)hs & 15) &&
+        (long long)E * 2 * ff < 2147483647LL && (long long)E * d < 2147483647LL) {
+        // many rows an expert: the tcgen05 tiles
+        alignas(64) CUtensorMap ta1, tw1, ta2, tw2;
+        int st = kp_make_map_bf16_2d(&ta1, hs, (unsigned long long)pairs, d, d, MT_BK, MOE_BIG);
+        if (!st) st = kp_make_map_bf16_2d(&tw1, w_gu, (unsigned long long)E * 2 * ff, d, d, MT_BK, MT_BN / 2);
+        if (!st) st = kp_make_map_bf16_2d(&ta2, act, (unsigned long long)pairs, ff, ff, MT_BK, MOE_BIG);
+        if (!st) st = kp_make_map_bf16_2d(&tw2, w_down, (unsigned long long)E * d, ff, ff, MT_BK, MT_BN);
+        if (st) return st;
+        const size_t smem = (size_t)MT_STAGES * (MT_A_BYTES + MT_B_BYTES) + (2 * MT_STAGES + 1) * 8 + 16 + 1024;
+        static bool ready = false;
+        if (!ready) {
+            if ((e0 = cudaFuncSetAttribute(moe_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e0;
+            if ((e0 = cudaFuncSetAttribute(moe_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e0;
+            ready = true;
+        }
+        size_t gg = ((size_t)pairs * (d / 8) + 255) / 256;
+        if (gg > 148 * 16) gg = 148 * 16;
+        kp_launch_pdl(moe_gather_rows_kernel, dim3((unsigned)gg), dim3(256), 0, s, (const bf16*)h, ldh, perm, (bf16*)hs, (int)pairs,
+                      d / 8, top);
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        MtArgs a1 = {offsets, big_start, E, d, ff, 2 * ff, ff, act, ff, act_kind};
+        kp_launch_pdl(moe_tc_kernel<true>, dim3((ff + MT_BN / 2 - 1) / (MT_BN / 2), (unsigned)big_tiles), dim3(MT_THREADS), smem, s,
+                      ta1, tw1, a1);
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+        MtArgs a2 = {offsets, big_start, E, ff, d, d, 0, y, d, 0};
+        kp_launch_pdl(moe_tc_kernel<false>, dim3((d + MT_BN - 1) / MT_BN, (unsigned)big_tiles), dim3(MT_THREADS), smem, s, ta2, tw2, a2);
+        if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;
+    } else if (tc) {
         kp_launch_pdl(moe_gate_up_tc_kernel, dim3((ff + MOE_TC_BN - 1) / MOE_TC_BN, max_tiles), dim3(128), 0, s, (const bf16*)h,
                       ldh, (const bf16*)w_gu, offsets, tile_start, perm, (bf16*)act, E, top, d, ff, act_kind);
         if ((e0 = cudaGetLastError()) != cudaSuccess) return (int)e0;

@@ -80,17 +80,18 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
     for (int i = lane; i < hd; i += 32) dst[i] = from_f32<T>(x[i]);
 }
 
-// The same for bfloat16 with head size 64 or 128, full NeoX rotation (or none) and 16-byte aligned rows: a
-// thread holds 8 consecutive elements of a head (one 16-byte load and one 16-byte store), hd / 8 lanes share
-// a head; the sum of squares and the rotation partner (element i + hd/2: the lane hd/16 further on) come by
-// warp shuffles.  Same arithmetic in the same order as the general kernel.
+// The same for bfloat16 with head size 64 or 128, NeoX rotation of the first `rot` dimensions (rot / 16 a power
+// of two; or none) and 16-byte aligned rows: a thread holds 8 consecutive elements of a head (one 16-byte load
+// and one 16-byte store), hd / 8 lanes share a head; the sum of squares and the rotation partner (element
+// i + rot/2: the lane rot/16 further on) come by warp shuffles.  Same arithmetic in the same order as the
+// general kernel.
 template <int HD>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __restrict__ q_w,
                            const float* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                            const float* __restrict__ sin_tab, const int* __restrict__ positions,
                            const int* __restrict__ slot_map, bf16* __restrict__ q_out, int ldq,
-                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv, int v_col) {
+                           bf16* __restrict__ cache, int page_size, int H, int G, int write_kv, int v_col, int rot) {
     kp_pdl_begin_early();
     constexpr int L = HD / 8;                          // lanes a head
     constexpr int HPB = 128 / L;                       // heads a block
@@ -123,16 +124,18 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
         for (int i = 0; i < 8; i++) x[i] = (x[i] * scale) * ww[i];
     }
     if (cos_tab != nullptr) {                          // every lane takes part in the shuffles
-        const bool lower = lane_in < L / 2;            // holds the `a` of its pairs; the partner holds `b`
-        const size_t tb = (size_t)positions[row] * (HD / 2) + (size_t)(lane_in % (L / 2)) * 8;
+        const int rl = rot >> 4;                       // lanes that hold one half of the rotated dimensions
+        const bool lower = lane_in < rl;               // holds the `a` of its pairs; the partner holds `b`
+        const bool rotated = lane_in < 2 * rl;         // (the lanes behind pass their elements on unchanged)
+        const size_t tb = (size_t)positions[row] * (rot >> 1) + (size_t)(lane_in % rl) * 8;
         const float4 c0 = __ldg(reinterpret_cast<const float4*>(cos_tab + tb)), c1 = __ldg(reinterpret_cast<const float4*>(cos_tab + tb) + 1);
         const float4 s0 = __ldg(reinterpret_cast<const float4*>(sin_tab + tb)), s1 = __ldg(reinterpret_cast<const float4*>(sin_tab + tb) + 1);
         const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[i], L / 2);
-            if (kind != 2) x[i] = lower ? x[i] * cc[i] - other * sn[i] : other * sn[i] + x[i] * cc[i];
+            const float other = __shfl_xor_sync(0xffffffffu, x[i], rl);
+            if (kind != 2 && rotated) x[i] = lower ? x[i] * cc[i] - other * sn[i] : other * sn[i] + x[i] * cc[i];
         }
     }
     if (!live || (kind != 0 && !write_kv)) return;
@@ -165,8 +168,10 @@ extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, con
     if (hd < 2 || hd > KP_MAX_HEAD_DIM || (hd & 1)) return KP_ERR_UNSUPPORTED;
     if (cos_tab && (rot < 2 || rot > hd || (rot & 1))) return KP_ERR_BAD_ARG;
     if (n > 65535) return KP_ERR_UNSUPPORTED;
-    // the 16-byte form: bfloat16, head size 64 or 128, whole-head NeoX rotation or none, aligned rows
-    if (dtype == KP_DTYPE_BF16 && (hd == 64 || hd == 128) && q_out != nullptr && (!cos_tab || (rot == hd && !interleaved)) &&
+    // the 16-byte form: bfloat16, head size 64 or 128, NeoX rotation of 16, 32, 64 or 128 dimensions or none, aligned rows
+    const bool rot_ok = !cos_tab || (!interleaved && (rot == 16 || rot == 32 || rot == 64 || rot == 128) && rot <= hd);
+    if (!cos_tab) rot = hd;
+    if (dtype == KP_DTYPE_BF16 && (hd == 64 || hd == 128) && q_out != nullptr && rot_ok &&
         (ld % 8 == 0) && (ldq % 8 == 0) && (v_col % 8 == 0) && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15) &&
         (!q_w || !((uintptr_t)q_w & 15)) && (!k_w || !((uintptr_t)k_w & 15)) &&
         (!cos_tab || (!((uintptr_t)cos_tab & 15) && !((uintptr_t)sin_tab & 15)))) {
@@ -174,10 +179,10 @@ extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, con
         dim3 vgrid((H + 2 * G + hpb - 1) / hpb, n);
         if (hd == 64)
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<64>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot);
         else
             kp_launch_pdl(qk_norm_rope_kv_vec_kernel<128>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream, (const bf16*)qkv, ld, q_w,
-                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col);
+                          k_w, eps, cos_tab, sin_tab, positions, slot_map, (bf16*)q_out, ldq, (bf16*)cache, page_size, H, G, write_kv, v_col, rot);
         return kp_launch_status();
     }
     dim3 grid((H + 2 * G + 3) / 4, n);

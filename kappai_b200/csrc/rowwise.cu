@@ -194,6 +194,47 @@ postnorm_rows_kernel(const float* acc, const float* __restrict__ w, float* x_out
     }
 }
 
+// The same for 16-byte aligned rows of at most 8192 floats (d % 4 == 0): a thread keeps its float4s of the row in
+// registers, so the row is read once and leaves in 16- and 8-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(256)
+postnorm_rows_vec_kernel(const float* acc, const float* __restrict__ w, float* x_out, T* h_out, float* scaled_out,
+                         int d, float eps, float alpha) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(acc + (size_t)r * d);
+    const int n4 = d >> 2;
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 ww = __ldg(w4 + i);
+            const float a = (v[j].x * scale) * ww.x, b = (v[j].y * scale) * ww.y, c = (v[j].z * scale) * ww.z,
+                        e = (v[j].w * scale) * ww.w;
+            const size_t o = (size_t)r * d + 4 * (size_t)i;
+            if (x_out) store4(x_out + o, a, b, c, e);
+            if (h_out) store4(h_out + o, a, b, c, e);
+            if (scaled_out) store4(scaled_out + o, alpha * a, alpha * b, alpha * c, alpha * e);
+        }
+    }
+}
+
 // The entry of such a layer when nothing has prepared it: h = x in the storage type, scaled = alpha * x.
 template <typename T>
 __global__ void scale_cast_kernel(const float* __restrict__ x, T* __restrict__ h_out, float* __restrict__ scaled_out,
@@ -217,6 +258,25 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ o, int ldo, const T* __restr
         const float z = to_f32(g[r * ldg + c]);
         T* p = o + r * ldo + c;
         *p = from_f32<T>(to_f32(*p) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+// The same, eight bfloat16 a thread, for 16-byte aligned rows whose length is a multiple of 8.
+__global__ void sigmoid_gate_vec_kernel(bf16* __restrict__ o, int ldo, const bf16* __restrict__ g, int ldg, int n, int cols8) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * cols8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols8, c = (i % cols8) * 8;
+        uint4 ov = *reinterpret_cast<const uint4*>(o + r * ldo + c);
+        const uint4 gv = *reinterpret_cast<const uint4*>(g + r * ldg + c);
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 a = __bfloat1622float2(o2[j]), z = __bfloat1622float2(g2[j]);
+            o2[j] = __floats2bfloat162_rn(a.x * (1.0f / (1.0f + expf(-z.x))), a.y * (1.0f / (1.0f + expf(-z.y))));
+        }
+        *reinterpret_cast<uint4*>(o + r * ldo + c) = ov;
     }
 }
 
@@ -326,6 +386,13 @@ int kp_postnorm_rows(const float* acc, const float* w, float* x_out, void* h_out
                      float eps, float alpha, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (d < 1) return KP_ERR_BAD_ARG;
+    // (which kernel runs depends on the row's size and alignment only, never on the batch)
+    if ((d & 3) == 0 && d <= 8192 &&
+        (((uintptr_t)acc | (uintptr_t)w | (uintptr_t)x_out | (uintptr_t)h_out | (uintptr_t)scaled_out) & 15) == 0) {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(postnorm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, acc, w,
+                                                   x_out, (T*)h_out, scaled_out, d, eps, alpha)));
+        return kp_launch_status();
+    }
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(postnorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, acc, w, x_out,
                                                (T*)h_out, scaled_out, d, eps, alpha)));
     return kp_launch_status();
@@ -341,6 +408,11 @@ int kp_scale_cast(const float* x, void* h_out, float* scaled_out, long long n, f
 
 int kp_sigmoid_gate(void* o, int ldo, const void* g, int ldg, int n, int cols, int dtype, void* stream) {
     if (n <= 0 || cols <= 0) return 0;
+    if (dtype == KP_DTYPE_BF16 && cols % 8 == 0 && ldo % 8 == 0 && ldg % 8 == 0 && !(((uintptr_t)o | (uintptr_t)g) & 15)) {
+        kp_launch_pdl(sigmoid_gate_vec_kernel, dim3(grid_for((size_t)n * (cols / 8), 256)), dim3(256), 0, (cudaStream_t)stream,
+                      (bf16*)o, ldo, (const bf16*)g, ldg, n, cols / 8);
+        return kp_launch_status();
+    }
     const int gr = grid_for((size_t)n * cols, 256);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(sigmoid_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo,
                                                (const T*)g, ldg, n, cols)));

@@ -173,7 +173,7 @@ def _rows_2d(t: torch.Tensor, name: str) -> int:
 # issuing work and returns.  The engine reads the words of a step with the step's own device-to-host copy.
 
 _STATUS_LIBS = (("gemm_tc", "tc"), ("gemm_stream", "stream"), ("attention_mma", "attention_mma"),
-                ("attention_tc", "attention_tc"))
+                ("attention_tc", "attention_tc"), ("moe", "moe_tc"))
 
 
 def read_status() -> dict:
@@ -818,7 +818,7 @@ MOE_MAX_EXPERTS = 1536     # experts the routing kernels hold in shared memory
 
 def moe_layout_ints(n: int, E: int, top: int) -> int:
     """int32 words of the device-side layout of one step (see :func:`moe_route`)."""
-    return 2 * (E + 1) + 2 * n * top
+    return 3 * (E + 1) + 2 * n * top
 
 
 def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.Tensor, layout: torch.Tensor) -> None:
@@ -834,6 +834,49 @@ def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.
     if idx.numel() != n * top or weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
         raise KernelError("moe_route: output sizes")
     _run("moe_route", load_library("moe").kp_moe_route, _ptr(logits), n, E, top, _ptr(idx), _ptr(weights), _ptr(layout), STREAM)
+    LAUNCHES[0] += 1
+
+
+MOE_TC_MIN_PAIRS = [512]   # (row, expert) pairs of a step from which the experts' products run on tcgen05 tiles
+
+
+def moe_set_tc_min_pairs(v: int) -> None:
+    """For measurements and tests: the number of pairs from which the tcgen05 path is taken."""
+    MOE_TC_MIN_PAIRS[0] = int(v)
+    load_library("moe").kp_moe_set_tc_min_pairs(ctypes.c_longlong(int(v)))
+
+
+def moe_tc_status() -> int:
+    return _read_one("moe", "moe_tc")
+
+
+MOE_ROUTER_ROWS = 4        # rows a block of the fused router keeps in shared memory
+
+
+def moe_router_ok(d: int, E: int) -> bool:
+    """Can the fused router kernel take rows of ``d`` elements and ``E`` experts?"""
+    return d % 4 == 0 and E <= MOE_MAX_EXPERTS and MOE_ROUTER_ROWS * (d + E) * 4 <= 200 * 1024
+
+
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+               weights: torch.Tensor, layout: torch.Tensor) -> None:
+    """The router in one go: logits ``h w_router^T + bias`` in float32 (``w_router`` [E, d] and ``bias`` are float32;
+    ``h`` is widened from its storage type), the choice and the layout as :func:`moe_route` leaves them."""
+    _need(h, "h", contiguous=False); _need(w_router, "w_router", torch.float32)
+    _need(idx, "idx", torch.int32); _need(weights, "weights", torch.float32); _need(layout, "layout", torch.int32)
+    n, d = h.shape
+    E = w_router.shape[0]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != E:
+            raise KernelError("moe_router: bias size")
+    if w_router.shape[1] != d or not moe_router_ok(d, E) or not (1 <= top <= min(E, MOE_MAX_TOP)):
+        raise KernelError("moe_router: sizes not supported")
+    if idx.numel() != n * top or weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
+        raise KernelError("moe_router: output sizes")
+    _run("moe_router", load_library("moe").kp_moe_router, _ptr(h), _rows_2d(h, "h"), _ptr(w_router), _ptr(bias), n, E, d, top,
+         _ptr(idx), _ptr(weights), _ptr(layout), dtype_code(h.dtype), STREAM,
+         work=(2 * n * E * d, n * d * h.element_size() + E * d * 4))
     LAUNCHES[0] += 1
 
 
@@ -853,8 +896,11 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         raise KernelError("moe_experts: routing tables do not fit")
     act = torch.empty((n * top, ff), dtype=h.dtype, device=h.device)
     y = torch.empty((n * top, d), dtype=torch.float32, device=h.device)
+    # (many rows, 16-bit: the tcgen05 tiles read the rows laid out place by place)
+    hs = torch.empty((n * top, d), dtype=h.dtype, device=h.device) if (h.dtype == torch.bfloat16 and n * top >= MOE_TC_MIN_PAIRS[0]) else None
     _run("moe_experts", load_library("moe").kp_moe_experts, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate_up), _ptr(w_down), _ptr(layout),
-         _ptr(weights), _ptr(act), _ptr(y), _ptr(out), n, E, top, d, ff, activation_code(activation), dtype_code(h.dtype),
-         STREAM, tag=f" {E}x{ff}x{d}", work=(6 * n * top * ff * d, 0))
+         _ptr(weights), _ptr(act), _ptr(y), _ptr(out), _ptr(hs), n, E, top, d, ff, activation_code(activation), dtype_code(h.dtype),
+         STREAM, tag=f" {E}x{ff}x{d}",
+         work=(6 * n * top * ff * d, min(E, n * top) * 3 * ff * d * h.element_size()))     # (bytes: the experts a step can touch)
     LAUNCHES[0] += 2
     return out

@@ -98,11 +98,14 @@ class MixtureOfExperts(Part):
 
     def forward(self, h, residual, ctx):
         n = h.shape[0]
-        logits = linear(h, self.w_router, self.b_router, out_dtype=torch.float32)
         idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
         layout = torch.empty(K.moe_layout_ints(n, self.E, self.top), dtype=torch.int32, device=h.device)
-        K.moe_route(logits, self.top, idx, weights, layout)
+        if K.moe_router_ok(self.d, self.E) and h.stride(1) == 1:
+            K.moe_router(h, self.w_router, self.b_router, self.top, idx, weights, layout)
+        else:
+            logits = linear(h, self.w_router, self.b_router, out_dtype=torch.float32)
+            K.moe_route(logits, self.top, idx, weights, layout)
         K.moe_experts(h, self.w_gu, self.w_down, layout, weights, self.top, residual, self.activation)
 
 

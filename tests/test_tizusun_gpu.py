@@ -36,7 +36,7 @@ def tiz_plain(tiz_dirs):
 
 # ------------------------------------------------------------------------------------- mechanisms alone
 
-@pytest.mark.parametrize("n,d", [(1, 48), (5, 320), (300, 36), (3, 2500)])
+@pytest.mark.parametrize("n,d", [(1, 48), (5, 320), (300, 36), (3, 2500), (2, 9000), (4, 37)])
 def test_postnorm_rows(n, d):
     from kappai_b200.ops import kernels as K
     rng = np.random.default_rng(d)
@@ -59,11 +59,12 @@ def test_sigmoid_gate_reads_columns_of_a_wider_row():
     from kappai_b200.ops import kernels as K
     rng = np.random.default_rng(1)
     for dt, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
-        o, wide = rng.normal(0, 1, (7, 40)), rng.normal(0, 2, (7, 100))
-        od, wd = dev(o, dt), dev(wide, dt)
-        K.sigmoid_gate(od, wd[:, 50:90])
-        want = od.float().cpu().numpy() * 0 + (dev(o, dt).float().cpu().numpy() * P.sigmoid(wd[:, 50:90].float().cpu().numpy()))
-        assert np.abs(od.float().cpu().numpy() - want).max() <= tol
+        for c0 in (50, 56):                                     # columns that are not, and that are, 16-byte aligned
+            o, wide = rng.normal(0, 1, (7, 40)), rng.normal(0, 2, (7, 104))
+            od, wd = dev(o, dt), dev(wide, dt)
+            K.sigmoid_gate(od, wd[:, c0:c0 + 40])
+            want = dev(o, dt).float().cpu().numpy() * P.sigmoid(wd[:, c0:c0 + 40].float().cpu().numpy())
+            assert np.abs(od.float().cpu().numpy() - want).max() <= tol
 
 
 @pytest.mark.parametrize("act", ["relu", "silu", "gelu_tanh"])
@@ -90,7 +91,8 @@ def test_relu_in_the_products_gated_epilogue(M, K_, ff):
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,hd,rot", [(4, 2, 32, 16), (3, 1, 48, 48), (10, 1, 24, 12), (4, 1, 64, 64), (2, 2, 128, 128)])
+@pytest.mark.parametrize("H,G,hd,rot", [(4, 2, 32, 16), (3, 1, 48, 48), (10, 1, 24, 12), (4, 1, 64, 64), (2, 2, 128, 128),
+                                        (4, 2, 64, 32), (3, 1, 64, 16), (2, 1, 128, 64), (2, 1, 128, 48), (5, 1, 64, 8)])
 def test_qk_kernel_takes_the_values_from_the_key_columns(H, G, hd, rot, dt):
     from kappai_b200.ops import kernels as K
     rng = np.random.default_rng(hd)
@@ -237,10 +239,15 @@ def test_tiled_prompt_kernels_keep_to_the_block(H, G, hd, page, block, variant):
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,E,top,d,ff", [(1, 4, 2, 32, 16), (5, 6, 1, 64, 24), (70, 3, 2, 48, 40), (33, 8, 8, 40, 12),
-                                          (200, 16, 3, 128, 64), (9, 5, 2, 36, 10)])
-def test_mixture_kernels_against_plain(n, E, top, d, ff, dt):
+@pytest.mark.parametrize("n,E,top,d,ff,force_tc", [
+    (1, 4, 2, 32, 16, False), (5, 6, 1, 64, 24, False), (70, 3, 2, 48, 40, False), (33, 8, 8, 40, 12, False),
+    (200, 16, 3, 128, 64, False), (9, 5, 2, 36, 10, False),
+    (300, 4, 2, 128, 64, True), (700, 3, 1, 200, 72, True), (40, 6, 2, 64, 136, True), (1000, 16, 4, 256, 192, True)])
+def test_mixture_kernels_against_plain(n, E, top, d, ff, force_tc, dt):
+    """The last cases run the grouped tcgen05 tiles in 16 bits (experts with more rows than a tile, with fewer, with
+    none; widths and expert sizes that are no multiple of the tile), the others the mma.sync and CUDA-core tiles."""
     from kappai_b200.ops import kernels as K
+    K.moe_set_tc_min_pairs(1 if force_tc else 1 << 40)
     rng = np.random.default_rng(n * E)
     h = bf16_round(rng.normal(0, 1, (n, d)))
     w = {"router": bf16_round(rng.normal(0, 3 / math.sqrt(d), (E, d))), "router.b": bf16_round(rng.normal(0, 0.5, E))}
@@ -257,14 +264,21 @@ def test_mixture_kernels_against_plain(n, E, top, d, ff, dt):
     assert np.array_equal(idx.cpu().numpy(), want_idx)
     assert np.abs(wts.cpu().numpy() - want_w).max() < 1e-5
     lay = layout.cpu().numpy()
-    offsets, perm, inv = lay[:E + 1], lay[2 * (E + 1):2 * (E + 1) + n * top], lay[2 * (E + 1) + n * top:]
+    offsets, perm, inv = lay[:E + 1], lay[3 * (E + 1):3 * (E + 1) + n * top], lay[3 * (E + 1) + n * top:]
     assert offsets[E] == n * top and sorted(perm.tolist()) == list(range(n * top)) and np.array_equal(perm[inv], np.arange(n * top))
     assert all(want_idx.reshape(-1)[perm[p]] == e for e in range(E) for p in range(offsets[e], offsets[e + 1]))
+    if K.moe_router_ok(d, E):                                                     # the same from the fused router
+        idx2, wts2, layout2 = torch.empty_like(idx), torch.empty_like(wts), torch.empty_like(layout)
+        K.moe_router(dev(h, dt), dev(w["router"]), dev(w["router.b"]), top, idx2, wts2, layout2)
+        assert torch.equal(idx2, idx) and (wts2 - wts).abs().max().item() < 1e-5
+        assert torch.equal(layout2[:3 * (E + 1)], layout[:3 * (E + 1)])
     base = rng.normal(0, 1, (n, d)).astype(np.float32)
     out = dev(base)
     w_gu = torch.stack([torch.cat([dev(w[f"e{e}.gate"], dt), dev(w[f"e{e}.up"], dt)], 0) for e in range(E)]).contiguous()
     w_dn = torch.stack([dev(w[f"e{e}.down"], dt) for e in range(E)]).contiguous()
     K.moe_experts(dev(h, dt), w_gu, w_dn, layout, wts, top, out, "silu")
+    K.moe_set_tc_min_pairs(512)
+    assert K.moe_tc_status() == 0
     want = base + P.mixture(h, w, E, top, "silu")
     err = np.abs(out.cpu().numpy() - want).max()
     assert err < (3e-5 if dt == torch.float32 else 4e-2), err
