@@ -40,12 +40,14 @@ def _ceil_div(a: int, b: int) -> int:
 class PagePool:
     """Pages of one layer group."""
 
-    def __init__(self, n_pages: int, page_size: int, window: Optional[int] = None):
+    def __init__(self, n_pages: int, page_size: int, window: Optional[int] = None, block: Optional[int] = None):
         if n_pages < 1 or page_size < 1:
             raise CacheError("a page pool needs at least one page and a positive page size")
         if window is not None and window < 1:
             raise CacheError("window must be positive")
-        self.n_pages, self.page_size, self.window = n_pages, page_size, window
+        if block is not None and block < 1:
+            raise CacheError("block must be positive")
+        self.n_pages, self.page_size, self.window, self.block = n_pages, page_size, window, block
         self._free: List[int] = list(range(n_pages - 1, -1, -1))      # stack: lowest page first
         self._tables: Dict[Hashable, List[int]] = {}
         self._held: Dict[Hashable, int] = {}                          # pages currently held per request
@@ -103,12 +105,16 @@ class PagePool:
         self._version[req] = self._stamp()
 
     def release_behind(self, req: Hashable, next_pos: int) -> int:
-        """Windowed groups: give back pages whose every key lies before the
-        window of position ``next_pos`` (the next token to run) and hence of
-        all later ones.  Returns the number of pages released."""
-        if self.window is None:
-            return 0
-        first_needed = next_pos - self.window + 1
+        """Groups with a window or with blocks of positions: give back pages
+        whose every key lies before the window of position ``next_pos`` (the
+        next token to run), or before the start of that position's block, and
+        hence out of reach of all later positions too.  Returns the number of
+        pages released."""
+        first_needed = 0
+        if self.window is not None:
+            first_needed = next_pos - self.window + 1
+        if self.block is not None:
+            first_needed = max(first_needed, (next_pos // self.block) * self.block)
         if first_needed <= 0:
             return 0
         t = self._tables[req]
@@ -201,7 +207,8 @@ class RequestCache:
 class CacheManager:
     """All page groups and the slot pool of one engine.
 
-    ``groups`` maps a group key to ``(n_pages, page_size, window)``.  Each
+    ``groups`` maps a group key to ``(n_pages, page_size, window)`` or
+    ``(n_pages, page_size, window, block)``.  Each
     request gets one slot (used by every state-holding layer) and one block
     table per group.
     """

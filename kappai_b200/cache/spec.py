@@ -21,10 +21,13 @@ class PagedKVSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # keys older than this many positions are never read again
+    block: Optional[int] = None       # a position reads no key from before its own block of this many positions
 
     @property
     def group_key(self) -> Tuple:
-        return ("kv", self.num_kv_heads, self.head_dim, self.window)
+        if self.block is None:
+            return ("kv", self.num_kv_heads, self.head_dim, self.window)
+        return ("kv", self.num_kv_heads, self.head_dim, self.window, ("block", self.block))
 
 
 @dataclass(frozen=True)

@@ -67,41 +67,58 @@ moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* _
 // The router as one kernel: logits z = h Wr^T + b in float32 (h is widened from its storage type; a row's
 // logit sums k in an order fixed by the lane pattern, whatever the batch), then the choice as above.  A block
 // takes MOE_RB rows, which stay in shared memory as float32 while each warp walks its experts' rows of Wr.
-#define MOE_RB 4
-template <typename T>
+// (RB rows a block: 8 for steps of many rows, so that Wr is fetched from L2 an eighth as often, 1 for steps of few,
+// so that every row has a block of its own.  A warp takes four of its experts at a time: their loads are in
+// flight together.  The order in which a (row, expert) logit adds up does not depend on RB.)
+template <typename T, int RB>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr, const float* __restrict__ bias, int n,
                   int E, int d, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
     kp_pdl_begin();
-    extern __shared__ __align__(16) float router_sm[];          // [MOE_RB][d] rows, [MOE_RB][E] logits
+    extern __shared__ __align__(16) float router_sm[];          // [RB][d] rows, [RB][E] logits
     float* hs = router_sm;
-    float* zs = router_sm + (size_t)MOE_RB * d;
+    float* zs = router_sm + (size_t)RB * d;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row0 = blockIdx.x * MOE_RB, nr = min(MOE_RB, n - row0);
-    for (int i = threadIdx.x; i < MOE_RB * d; i += blockDim.x) {
+    const int row0 = blockIdx.x * RB, nr = min(RB, n - row0);
+    for (int i = threadIdx.x; i < RB * d; i += blockDim.x) {
         const int r = i / d, k = i - r * d;
         hs[i] = r < nr ? to_f32(h[(size_t)(row0 + r) * ldh + k]) : 0.f;
     }
     __syncthreads();
-    for (int e = warp; e < E; e += 8) {
-        const float4* w4 = reinterpret_cast<const float4*>(wr + (size_t)e * d);
-        float acc[MOE_RB];
+    for (int e0 = warp; e0 < E; e0 += 32) {                     // experts e0, e0 + 8, e0 + 16, e0 + 24 of this warp
+        const float4* w4[4];
+        bool has[4];
 #pragma unroll
-        for (int r = 0; r < MOE_RB; r++) acc[r] = 0.f;
+        for (int j = 0; j < 4; j++) {
+            has[j] = e0 + 8 * j < E;
+            w4[j] = reinterpret_cast<const float4*>(wr + (size_t)(has[j] ? e0 + 8 * j : e0) * d);
+        }
+        float acc[4][RB];
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[j][r] = 0.f;
         for (int k = lane * 4; k < d; k += 128) {
-            const float4 w = __ldg(w4 + (k >> 2));
+            float4 w[4];
 #pragma unroll
-            for (int r = 0; r < MOE_RB; r++) {
+            for (int j = 0; j < 4; j++) w[j] = __ldg(w4[j] + (k >> 2));
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
                 const float4 x = *reinterpret_cast<const float4*>(hs + (size_t)r * d + k);
-                acc[r] = fmaf(x.x, w.x, acc[r]); acc[r] = fmaf(x.y, w.y, acc[r]);
-                acc[r] = fmaf(x.z, w.z, acc[r]); acc[r] = fmaf(x.w, w.w, acc[r]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[j][r] = fmaf(x.x, w[j].x, acc[j][r]); acc[j][r] = fmaf(x.y, w[j].y, acc[j][r]);
+                    acc[j][r] = fmaf(x.z, w[j].z, acc[j][r]); acc[j][r] = fmaf(x.w, w[j].w, acc[j][r]);
+                }
             }
         }
 #pragma unroll
-        for (int r = 0; r < MOE_RB; r++) {
-            const float v = warp_sum(acc[r]);
-            if (lane == 0) zs[(size_t)r * E + e] = v + (bias ? bias[e] : 0.f);
-        }
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
+                const float v = warp_sum(acc[j][r]);
+                if (lane == 0 && has[j]) zs[(size_t)r * E + e0 + 8 * j] = v + (bias ? bias[e0 + 8 * j] : 0.f);
+            }
     }
     __syncthreads();
     if (warp >= nr) return;
@@ -299,11 +316,11 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
 // ------------------------------------------------------------------------ products on the tensor cores
 // The same two products for bfloat16 with mma.sync m16n8k16 (float32 accumulation): a CTA of four warps
 // takes one row tile of 32 places and 64 output columns; warp w owns columns 16 w .. 16 w + 15 (two n-tiles)
-// of both 16-row halves.  Operands go through shared memory in k-blocks of 32 (rows padded to 40 halves: the
+// of both 16-row halves.  Operands go through shared memory in k-blocks of 64 (rows padded to 72 halves: the
 // fragment loads of a warp then fall into different banks).  Needs K % 8 == 0 (16-byte loads).
 #define MOE_TC_BN 64
-#define MOE_TC_BK 32
-#define MOE_TC_LD 40
+#define MOE_TC_BK 64
+#define MOE_TC_LD 72
 
 __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -311,16 +328,32 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, cons
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// One k-block of NB operand matrices of `rows` rows each into shared memory (16 bytes a thread and turn);
-// rows beyond `valid` (or with a negative source row) and columns beyond K are zero.
-__device__ __forceinline__ void moe_tc_stage(bf16 (*dst)[MOE_TC_LD], int rows, const bf16* src, const int* src_rows,
-                                             long long ld, int first_row, int valid, int k0, int K) {
-    for (int el = threadIdx.x; el < rows * (MOE_TC_BK / 8); el += blockDim.x) {
+// One k-block of an operand matrix of ROWS rows: first from global memory into registers (16 bytes a thread and
+// turn; rows beyond `valid`, or with a negative source row, and columns beyond K are zero), later from the
+// registers into shared memory.  Between the two the products of the block before run, so that the loads'
+// latency passes under them (a CTA of a decode step has a handful of rows and lives on that latency).
+template <int ROWS>
+struct MoeFrag { uint4 v[ROWS * (MOE_TC_BK / 8) / 128]; };
+
+template <int ROWS>
+__device__ __forceinline__ void moe_tc_fetch(MoeFrag<ROWS>& f, const bf16* src, const int* src_rows, long long ld,
+                                             int first_row, int valid, int k0, int K) {
+#pragma unroll
+    for (int i = 0; i < ROWS * (MOE_TC_BK / 8) / 128; i++) {
+        const int el = threadIdx.x + i * 128;
         const int r = el / (MOE_TC_BK / 8), c8 = (el % (MOE_TC_BK / 8)) * 8;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        long long sr = src_rows ? (long long)src_rows[r] : (r < valid ? (long long)first_row + r : -1);
+        const long long sr = src_rows ? (long long)src_rows[r] : (r < valid ? (long long)first_row + r : -1);
         if (sr >= 0 && k0 + c8 < K) v = *reinterpret_cast<const uint4*>(src + sr * ld + k0 + c8);
-        *reinterpret_cast<uint4*>(&dst[r][c8]) = v;
+        f.v[i] = v;
+    }
+}
+template <int ROWS>
+__device__ __forceinline__ void moe_tc_put(bf16 (*dst)[MOE_TC_LD], const MoeFrag<ROWS>& f) {
+#pragma unroll
+    for (int i = 0; i < ROWS * (MOE_TC_BK / 8) / 128; i++) {
+        const int el = threadIdx.x + i * 128;
+        *reinterpret_cast<uint4*>(&dst[el / (MOE_TC_BK / 8)][(el % (MOE_TC_BK / 8)) * 8]) = f.v[i];
     }
 }
 
@@ -369,11 +402,21 @@ moe_gate_up_tc_kernel(const bf16* __restrict__ h, int ldh, const bf16* __restric
     const bf16* wu = wg + (size_t)ff * d;
     const int w_valid = min(MOE_TC_BN, ff - n0);
     float ag[2][2][4] = {}, au[2][2][4] = {};
+    MoeFrag<MOE_BM> fa;
+    MoeFrag<MOE_TC_BN> fg, fu;
+    moe_tc_fetch(fa, h, src_row, ldh, 0, 0, 0, d);
+    moe_tc_fetch(fg, wg, nullptr, d, n0, w_valid, 0, d);
+    moe_tc_fetch(fu, wu, nullptr, d, n0, w_valid, 0, d);
     for (int k0 = 0; k0 < d; k0 += MOE_TC_BK) {
-        moe_tc_stage(As, MOE_BM, h, src_row, ldh, 0, 0, k0, d);
-        moe_tc_stage(Gs, MOE_TC_BN, wg, nullptr, d, n0, w_valid, k0, d);
-        moe_tc_stage(Us, MOE_TC_BN, wu, nullptr, d, n0, w_valid, k0, d);
+        moe_tc_put(As, fa);
+        moe_tc_put(Gs, fg);
+        moe_tc_put(Us, fu);
         __syncthreads();
+        if (k0 + MOE_TC_BK < d) {                    // the next block is on its way while this one is multiplied
+            moe_tc_fetch(fa, h, src_row, ldh, 0, 0, k0 + MOE_TC_BK, d);
+            moe_tc_fetch(fg, wg, nullptr, d, n0, w_valid, k0 + MOE_TC_BK, d);
+            moe_tc_fetch(fu, wu, nullptr, d, n0, w_valid, k0 + MOE_TC_BK, d);
+        }
         moe_tc_block(ag, As, Gs, warp, lane);
         moe_tc_block(au, As, Us, warp, lane);
         __syncthreads();
@@ -406,10 +449,18 @@ moe_down_tc_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w_down
     const bf16* wd = w_down + (size_t)e * d * ff;
     const int w_valid = min(MOE_TC_BN, d - n0);
     float acc[2][2][4] = {};
+    MoeFrag<MOE_BM> fa;
+    MoeFrag<MOE_TC_BN> fw;
+    moe_tc_fetch(fa, act, nullptr, ff, row0, row1 - row0, 0, ff);
+    moe_tc_fetch(fw, wd, nullptr, ff, n0, w_valid, 0, ff);
     for (int k0 = 0; k0 < ff; k0 += MOE_TC_BK) {
-        moe_tc_stage(As, MOE_BM, act, nullptr, ff, row0, row1 - row0, k0, ff);
-        moe_tc_stage(Ws, MOE_TC_BN, wd, nullptr, ff, n0, w_valid, k0, ff);
+        moe_tc_put(As, fa);
+        moe_tc_put(Ws, fw);
         __syncthreads();
+        if (k0 + MOE_TC_BK < ff) {
+            moe_tc_fetch(fa, act, nullptr, ff, row0, row1 - row0, k0 + MOE_TC_BK, ff);
+            moe_tc_fetch(fw, wd, nullptr, ff, n0, w_valid, k0 + MOE_TC_BK, ff);
+        }
         moe_tc_block(acc, As, Ws, warp, lane);
         __syncthreads();
     }
@@ -666,17 +717,23 @@ int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, in
                   float* weights, int* layout, int dtype, void* stream) {
     if (n <= 0) return 0;
     if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return KP_ERR_UNSUPPORTED;
-    const size_t sm = ((size_t)MOE_RB * d + (size_t)MOE_RB * E) * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
+    const size_t sort_sm = ((size_t)3 * E + 1) * sizeof(int);
+    // eight rows a block where there are many and they fit shared memory, else one
+    const int rb = (n > 64 && ((size_t)8 * (d + E)) * sizeof(float) <= 200 * 1024) ? 8 : 1;
+    const size_t sm = ((size_t)rb * d + (size_t)rb * E) * sizeof(float);
     if ((d & 3) || ((uintptr_t)wr & 15) || sm > 200 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    KP_DISPATCH_DTYPE(dtype, T, {
-        if (sm > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            if (e != cudaSuccess) return (int)e;
-        }
-        kp_launch_pdl(moe_router_kernel<T>, dim3((n + MOE_RB - 1) / MOE_RB), dim3(256), sm, s, (const T*)h, ldh, wr, bias, n, E, d,
-                      top, idx, weights);
-    });
+#define MOE_ROUTER_LAUNCH(T, RB)                                                                                          \
+    do {                                                                                                                  \
+        if (sm > 48 * 1024) {                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<T, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+            if (e != cudaSuccess) return (int)e;                                                                          \
+        }                                                                                                                 \
+        kp_launch_pdl(moe_router_kernel<T, RB>, dim3((n + RB - 1) / RB), dim3(256), sm, s, (const T*)h, ldh, wr, bias, n, E, d, \
+                      top, idx, weights);                                                                                 \
+    } while (0)
+    KP_DISPATCH_DTYPE(dtype, T, { if (rb == 8) MOE_ROUTER_LAUNCH(T, 8); else MOE_ROUTER_LAUNCH(T, 1); });
+#undef MOE_ROUTER_LAUNCH
     cudaError_t e0 = cudaGetLastError();
     if (e0 != cudaSuccess) return (int)e0;
     int* offsets = layout;

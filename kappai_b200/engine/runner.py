@@ -111,8 +111,8 @@ class ModelRunner:
         self.cache_plan = plan
         group_keys = list(needs)
         self.storage = CacheStorage(specs, borrowing, plan.pages, page_size, max_requests, self.dtype, self.device)
-        self.cache = CacheManager({gk: (plan.pages[gk], page_size, self.storage.groups[gk].window)
-                                   for gk in group_keys}, max_requests)
+        self.cache = CacheManager({gk: (plan.pages[gk], page_size, self.storage.groups[gk].window,
+                                        self.storage.groups[gk].block) for gk in group_keys}, max_requests)
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
         self.last_h2d_bytes = 0

@@ -850,12 +850,9 @@ def moe_tc_status() -> int:
     return _read_one("moe", "moe_tc")
 
 
-MOE_ROUTER_ROWS = 4        # rows a block of the fused router keeps in shared memory
-
-
 def moe_router_ok(d: int, E: int) -> bool:
-    """Can the fused router kernel take rows of ``d`` elements and ``E`` experts?"""
-    return d % 4 == 0 and E <= MOE_MAX_EXPERTS and MOE_ROUTER_ROWS * (d + E) * 4 <= 200 * 1024
+    """Can the fused router kernel take rows of ``d`` elements and ``E`` experts (a row and its logits in shared memory)?"""
+    return d % 4 == 0 and E <= MOE_MAX_EXPERTS and (d + E) * 4 <= 200 * 1024
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,

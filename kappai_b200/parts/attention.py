@@ -170,7 +170,7 @@ class Attention(Part):
             self.k_w = w["k_norm.weight"].float().contiguous()
 
     def cache_spec(self):
-        return PagedKVSpec(self.G, self.hd, self.window)
+        return PagedKVSpec(self.G, self.hd, self.window, None if self.block is None else int(self.block))
 
     def forward(self, h, residual, ctx, cache):
         """``cache``: a :class:`~kappai_b200.cache.storage.KVLayerView`."""

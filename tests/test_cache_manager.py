@@ -38,6 +38,35 @@ def test_pages_are_used_again():
     p.check()
 
 
+def test_blocks_of_positions_give_pages_back():
+    """A group whose positions read no key from before their own block: pages wholly before the block of the next
+    position go back, whatever the portions the request grew in; a window on top releases what either allows."""
+    p = PagePool(16, 4, block=10)
+    p.open("a")
+    p.extend("a", 9)
+    assert p.release_behind("a", 9) == 0            # next position 9 is still in block 0
+    p.extend("a", 10)
+    assert p.release_behind("a", 10) == 2           # next position 10 starts block 1 (keys 10..): pages 0, 1 hold keys 0..7
+    t = p.table("a")
+    assert t[:2] == [RELEASED] * 2 and t[2] != RELEASED      # page 2 holds keys 8..11: key 10 is still read
+    p.extend("a", 37)
+    assert p.release_behind("a", 37) == 5           # block 3 starts at 30: pages 2..6 (keys 8..27) are behind
+    p.check()
+    p.close("a")
+    assert p.n_free == 16
+    q = PagePool(16, 4, window=6, block=100)
+    q.open("a"); q.extend("a", 50)
+    assert q.release_behind("a", 50) == 11          # the window (keys 45..) releases more than the block (keys 0..)
+    m = CacheManager({"kv": (8, 4, None, 8)}, n_slots=2)
+    m.admit("a"); m.extend("a", 16); m.advance("a", 16)
+    assert m.pools["kv"].n_free == 8                # position 16 starts a block: keys 0..15 are out of reach for good
+    m.extend("a", 30); m.advance("a", 30)
+    assert m.pools["kv"].n_free == 8 - 2            # keys 24..31 are held; 16..23 lie before the block of position 30
+    for n in (44, 60, 75, 90):                      # a request far longer than the pool (32 keys) keeps running
+        m.extend("a", n); m.advance("a", n)
+    m.check()
+
+
 def test_window_gives_pages_back():
     p = PagePool(16, 4, window=6)
     p.open("a")
