@@ -51,7 +51,23 @@ TIZ_S = {"architecture": "Tizusun", "vocab": 300, "width": 128, "postln_alpha": 
            _MOE(8, 2, 64)),
 ]}
 
-CONFIGS = {"P": (TIZ_P, 3), "Q": (TIZ_Q, 4), "R": (TIZ_R, 5), "S": (TIZ_S, 6)}
+# T: widths at which the decode products stream their weights (K a multiple of 512) and the prompt products run on
+# tcgen05; head size 128 (mma.sync prompt kernel, split-key tensor-core decode), as many kv heads as heads, a block
+# as long as a page, rotation of half a head
+TIZ_T = {"architecture": "Tizusun", "vocab": 500, "width": 512, "postln_alpha": 2.5, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_attn(4, 4, 128, {"base": 50000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
+           _DENSE(1024)),
+    _layer(_attn(4, 4, 128, {"base": 50000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
+           _MOE(4, 2, 128)),
+]}
+# U: blocks of one position (a token reads itself alone) and of three, two experts of which one, a vocabulary smaller than a warp
+TIZ_U = {"architecture": "Tizusun", "vocab": 19, "width": 32, "postln_alpha": 1.25, "norm": {"eps": 1e-3}, "layers": [
+    _layer(_attn(2, 1, 16, {"base": 100.0, "dims": 16}, 1), _MOE(2, 1, 8)),
+    _layer(_attn(2, 2, 16, {"base": 100.0, "dims": 4}, 3), _DENSE(8)),
+    _layer(_attn(1, 1, 32, None, None), _MOE(2, 2, 40)),
+]}
+
+CONFIGS = {"P": (TIZ_P, 3), "Q": (TIZ_Q, 4), "R": (TIZ_R, 5), "S": (TIZ_S, 6), "T": (TIZ_T, 7), "U": (TIZ_U, 8)}
 
 
 def tensor_shapes(cfg):
