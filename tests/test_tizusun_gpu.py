@@ -431,3 +431,34 @@ def test_greedy_generation_through_the_engine(name, dtype, tiz_dirs, tiz_plain):
             best = int(np.argmax(lg[j]))
             assert t == best or lg[j][best] - lg[j][t] <= 4 * tol_for(dtype, lg[j]), (j, t, best)
     assert eng.runner.cache.slots.n_free == 4 and all(p.n_free == p.n_pages for p in eng.runner.cache.pools.values())
+
+
+def test_command_line_and_random_weights(tiz_dirs, tiz_plain, tmp_path):
+    """The command line runs the design like any other: greedy tokens equal the plain model's, --time names the
+    design's kernels, and --random-weights writes a loadable model folder from a Tizusun config.json."""
+    import json
+    import os
+    import subprocess
+    import sys
+    plain = tiz_plain["P"]
+    prompt = _requests(plain, [30], 77)["r0"]
+    cmd = [sys.executable, "-m", "kappai_b200.cli", "-m", tiz_dirs["P"], "-p", ",".join(map(str, prompt)), "-n", "12", "-t", "0",
+           "--fp32", "--time"]
+    p = subprocess.run(cmd, cwd=R.ROOT, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(t) for t in p.stdout.split()]
+    assert len(out) == 12
+    lg = plain.forward(prompt + out)[len(prompt) - 1:-1]
+    for j, t in enumerate(out):
+        best = int(np.argmax(lg[j]))
+        assert t == best or lg[j][best] - lg[j][t] <= 1e-4, (j, t, best)
+    for name in ("postnorm_rows", "moe_router", "moe_experts", "sigmoid_gate", "attention_split"):
+        assert name in p.stderr, (name, p.stderr[-3000:])
+    cfgp = tmp_path / "c.json"
+    cfgp.write_text(json.dumps(CONFIGS["Q"][0]))
+    made = tmp_path / "rw"
+    cmd = [os.path.join(R.ROOT, "bin", "kappai-cli"), "--random-weights", str(cfgp), "-s", "5", "-m", str(made), "-t", "0", "-n", "5",
+           "1 2 3"]
+    p = subprocess.run(cmd, cwd=str(tmp_path), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len(p.stdout.split()) == 5 and os.path.isfile(made / "model.safetensors")
