@@ -452,11 +452,14 @@ def run_design(a) -> int:
     import torch
     from kappai_b200 import ModelRunner, StepEntry
 
+    import kappai_b200.models.tizusun as tz
+    tz.SOFTMAX_WEIGHTS = a.softmax_weights
     pk = peaks()
     T, B, ctx_len = PROMPT_LEN, a.batch, PROMPT_LEN + 256
     warmup = max(a.warmup, 3)
     steps = min(a.steps, 128)
     out = {"design": "Tizusun", "beside": "LFM2 attention layers of the same sizes", "dtype": "bf16",
+           "softmax_weights": a.softmax_weights,
            "data": "synthetic: random weights, uniform random token ids", "prompt_tokens": T, "decode_batch": B,
            "decode_context": f"{T} to {ctx_len}", "peaks": pk, "sizes": {}}
     clocks = ClockSampler()
@@ -613,6 +616,10 @@ def main() -> int:
                     help="time another design at a few layer sizes beside LFM2 attention layers of the same sizes "
                          "(prefill, decode, device time by kernel class) instead of the default line")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only (e.g. 2048x32h64)")
+    ap.add_argument("--softmax-weights", choices=["float32", "operand"], default="float32",
+                    help="with --design tizusun: how the softmax weights meet the values: whole (the design's way: the "
+                         "mma.sync kernels multiply their three bfloat16 parts) or rounded to one bfloat16 operand (the "
+                         "tcgen05 prompt kernel can then run)")
     a = ap.parse_args()
 
     if a.impl == "reference":

@@ -60,6 +60,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Softmax weights in full: a float32 value is the exact sum of three bfloat16 parts (8 significant bits each), so
+// the product with V can be taken part by part on the tensor cores and added up in float32 without rounding the
+// weights.  Packs the next part of (a, b) and leaves in them what it did not take.
+__device__ __forceinline__ uint32_t pack_bf16_part(float& a, float& b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    a -= __low2float(h);
+    b -= __high2float(h);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // A tile in shared memory: 64 rows (keys) of HD bf16, as HD / 64 halves of 64 rows x 128 bytes; in a half the
 // 16-byte chunk c of row r lies at chunk c ^ (r & 7).  This is what a TMA box of 64 columns with the 128-byte
 // swizzle writes (tile on a 1024-byte boundary), so both ways of loading a tile give the same layout.
@@ -131,12 +141,13 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&
 // it, and a multiple of 8.  Boxes wholly outside the row's keys are not loaded; V rows outside them are zeroed.
 KP_STATUS_WORD(g_attn_status, attention_mma)          // 0 ok; 1: a bounded wait gave up
 
-template <int HD, int NW, bool TMA>
+template <int HD, int NW, bool TMA, bool EXACT>
 __global__ void __launch_bounds__(NW * 32)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
                       int n_chunks, float scale, int window, int page_size, int H, int G, int block) {
+    constexpr bool exact_p = EXACT;                               // the softmax weights enter the product with V whole
     kp_pdl_begin_early_if(gridDim.z > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -245,11 +256,13 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
     uint32_t pf[4][4];
 #pragma unroll
     for (int nt = 0; nt < 8; nt++) {
-        const float p0 = m == -INFINITY ? 0.f : expf(s[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(s[nt][1] - m);
-        // the sum runs over the values as they enter the product (rounded to bfloat16)
-        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        l += __low2float(pb) + __high2float(pb);
-        pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&pb);
+        float p0 = m == -INFINITY ? 0.f : expf(s[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(s[nt][1] - m);
+        // the sum runs over the values as they enter the product (rounded to bfloat16, or whole: see exact_p)
+        if (exact_p) l += p0 + p1;
+        const uint32_t pk = pack_bf16_part(p0, p1);
+        if (!exact_p) { const __nv_bfloat162 pb = *reinterpret_cast<const __nv_bfloat162*>(&pk); l += __low2float(pb) + __high2float(pb); }
+        s[nt][0] = p0; s[nt][1] = p1;                       // what the first part left
+        pf[nt >> 1][(nt & 1) * 2] = pk;
         pf[nt >> 1][(nt & 1) * 2 + 1] = 0;
     }
     l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -260,6 +273,14 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
 #pragma unroll
         for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
     pv_tile<HD>(o, pf, Vt, lane);
+    if (exact_p) {                                          // the weights' second and third parts
+#pragma unroll 1
+        for (int part = 0; part < 2; part++) {
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) pf[nt >> 1][(nt & 1) * 2] = pack_bf16_part(s[nt][0], s[nt][1]);
+            pv_tile<HD>(o, pf, Vt, lane);
+        }
+    }
 
     if (g < R) {
 #pragma unroll
@@ -321,12 +342,13 @@ static size_t ar_smem_bytes() {
            AR_GROUPS * sizeof(float) * (AR_NW * AM_RMAX * HD + 2 * AR_NW * AM_RMAX) + 32;
 }
 
-template <int HD>
+template <int HD, bool EXACT>
 __global__ void __launch_bounds__(AR_THREADS)
 attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                        const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
                        int n_chunks, float scale, int window, int page_size, int H, int G, int n_rows, int block) {
+    constexpr bool exact_p = EXACT;
     kp_pdl_begin_early_if(n_rows > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -493,11 +515,13 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
         uint32_t pf[4][4];
 #pragma unroll
         for (int nt = 0; nt < 8; nt++) {
-            const float p0 = m == -INFINITY ? 0.f : expf(sc[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(sc[nt][1] - m);
-            // the sum runs over the values as they enter the product (rounded to bfloat16)
-            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            l += __low2float(pb) + __high2float(pb);
-            pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&pb);
+            float p0 = m == -INFINITY ? 0.f : expf(sc[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(sc[nt][1] - m);
+            // the sum runs over the values as they enter the product (rounded to bfloat16, or whole: see exact_p)
+            if (exact_p) l += p0 + p1;
+            const uint32_t pk = pack_bf16_part(p0, p1);
+            if (!exact_p) { const __nv_bfloat162 pb = *reinterpret_cast<const __nv_bfloat162*>(&pk); l += __low2float(pb) + __high2float(pb); }
+            sc[nt][0] = p0; sc[nt][1] = p1;
+            pf[nt >> 1][(nt & 1) * 2] = pk;
             pf[nt >> 1][(nt & 1) * 2 + 1] = 0;
         }
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -508,6 +532,14 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
 #pragma unroll
             for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
         pv_tile<HD>(o, pf, Vt, lane);
+        if (exact_p) {                                                // the weights' second and third parts
+#pragma unroll 1
+            for (int part = 0; part < 2; part++) {
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) pf[nt >> 1][(nt & 1) * 2] = pack_bf16_part(sc[nt][0], sc[nt][1]);
+                pv_tile<HD>(o, pf, Vt, lane);
+            }
+        }
         __syncwarp();
         if (lane == 0) kp_mbar_arrive(&empty[s]);                     // this warp has read its tiles (and Q, and the item)
 
@@ -551,13 +583,14 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
 
 // ------------------------------------------------------------------ prefill (segments of many rows)
 // One CTA: 64 consecutive rows (tile `qt` of segment `seg`) of one head.  tile_seg / tile_q0 list the tiles.
-template <int HD>
+template <int HD, bool EXACT>
 __global__ void __launch_bounds__(128)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_rows,
                         const int* __restrict__ seg_pos, const int* __restrict__ tile_seg,
                         const int* __restrict__ tile_row0, bf16* __restrict__ out, int ldo, float scale, int window,
                         int page_size, int H, int G, int block) {
+    constexpr bool exact_p = EXACT;
     kp_pdl_begin();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [2][64][HD]
@@ -647,13 +680,18 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
             uint32_t pf[4][4];
 #pragma unroll
             for (int nt = 0; nt < 8; nt++) {
-                const float pa0 = mn_a == -INFINITY ? 0.f : expf(s[nt][0] - mn_a), pa1 = mn_a == -INFINITY ? 0.f : expf(s[nt][1] - mn_a);
-                const float pb0 = mn_b == -INFINITY ? 0.f : expf(s[nt][2] - mn_b), pb1 = mn_b == -INFINITY ? 0.f : expf(s[nt][3] - mn_b);
-                const __nv_bfloat162 xa = __floats2bfloat162_rn(pa0, pa1), xb = __floats2bfloat162_rn(pb0, pb1);
-                sa += __low2float(xa) + __high2float(xa);
-                sb += __low2float(xb) + __high2float(xb);
-                pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&xa);
-                pf[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&xb);
+                float pa0 = mn_a == -INFINITY ? 0.f : expf(s[nt][0] - mn_a), pa1 = mn_a == -INFINITY ? 0.f : expf(s[nt][1] - mn_a);
+                float pb0 = mn_b == -INFINITY ? 0.f : expf(s[nt][2] - mn_b), pb1 = mn_b == -INFINITY ? 0.f : expf(s[nt][3] - mn_b);
+                if (exact_p) { sa += pa0 + pa1; sb += pb0 + pb1; }
+                const uint32_t ka = pack_bf16_part(pa0, pa1), kb = pack_bf16_part(pb0, pb1);
+                if (!exact_p) {
+                    const __nv_bfloat162 xa = *reinterpret_cast<const __nv_bfloat162*>(&ka), xb = *reinterpret_cast<const __nv_bfloat162*>(&kb);
+                    sa += __low2float(xa) + __high2float(xa);
+                    sb += __low2float(xb) + __high2float(xb);
+                }
+                s[nt][0] = pa0; s[nt][1] = pa1; s[nt][2] = pb0; s[nt][3] = pb1;      // what the first part left
+                pf[nt >> 1][(nt & 1) * 2] = ka;
+                pf[nt >> 1][(nt & 1) * 2 + 1] = kb;
             }
             sa += __shfl_xor_sync(0xffffffffu, sa, 1); sa += __shfl_xor_sync(0xffffffffu, sa, 2);
             sb += __shfl_xor_sync(0xffffffffu, sb, 1); sb += __shfl_xor_sync(0xffffffffu, sb, 2);
@@ -662,6 +700,17 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
 #pragma unroll
             for (int dn = 0; dn < HD / 8; dn++) { o[dn][0] *= ca; o[dn][1] *= ca; o[dn][2] *= cb; o[dn][3] *= cb; }
             pv_tile<HD>(o, pf, Vs + buf * AM_TILE * HD, lane);
+            if (exact_p) {                                        // the weights' second and third parts
+#pragma unroll 1
+                for (int part = 0; part < 2; part++) {
+#pragma unroll
+                    for (int nt = 0; nt < 8; nt++) {
+                        pf[nt >> 1][(nt & 1) * 2] = pack_bf16_part(s[nt][0], s[nt][1]);
+                        pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16_part(s[nt][2], s[nt][3]);
+                    }
+                    pv_tile<HD>(o, pf, Vs + buf * AM_TILE * HD, lane);
+                }
+            }
         }
         __syncthreads();                                          // the buffer is free for the load after next
     }
@@ -696,7 +745,7 @@ static int am_n_sm() {
 template <int HD, int NW>
 static int launch_split(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
                         int max_blocks, const int* row_seg, const int* positions, float* part_acc, float* part_ml,
-                        int n_chunks, float scale, int window, int block, int page_size, int n, int H, int G, cudaStream_t s) {
+                        int n_chunks, float scale, int window, int block, int exact_p, int page_size, int n, int H, int G, cudaStream_t s) {
     const size_t smem = 1024 + (size_t)2 * NW * AM_TILE * HD * 2 + sizeof(float) * (NW * AM_RMAX * HD + 2 * NW * AM_RMAX) + 16;
     alignas(64) CUtensorMap tm = {};
     // tiles by TMA where the pages allow it (and the cache is known by its size), else by cp.async
@@ -710,19 +759,22 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
             const size_t rs = ar_smem_bytes<HD>();
             static bool ready = false;
             if (!ready) {
-                cudaError_t e = cudaFuncSetAttribute(attn_split_ring_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rs);
+                cudaError_t e = cudaFuncSetAttribute(attn_split_ring_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rs);
+                if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_split_ring_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rs);
                 if (e != cudaSuccess) return (int)e;
                 ready = true;
             }
             const long long items = (long long)n * G * n_chunks;
             const int sms = am_n_sm();
-            kp_launch_pdl(attn_split_ring_kernel<HD>, dim3((unsigned)(items < sms ? items : sms)), dim3(AR_THREADS), rs, s, tm,
+            kp_launch_pdl(exact_p ? attn_split_ring_kernel<HD, true> : attn_split_ring_kernel<HD, false>,
+                          dim3((unsigned)(items < sms ? items : sms)), dim3(AR_THREADS), rs, s, tm,
                           (const bf16*)q, ldq, block_table, max_blocks, row_seg, positions, part_acc, part_ml, n_chunks, scale,
                           window, page_size, H, G, n, block);
             return kp_launch_status();
         }
     }
-    auto kern = tma ? attn_split_mma_kernel<HD, NW, true> : attn_split_mma_kernel<HD, NW, false>;
+    auto kern = tma ? (exact_p ? attn_split_mma_kernel<HD, NW, true, true> : attn_split_mma_kernel<HD, NW, true, false>)
+                    : (exact_p ? attn_split_mma_kernel<HD, NW, false, true> : attn_split_mma_kernel<HD, NW, false, false>);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
@@ -736,11 +788,12 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
 template <int HD>
 static int launch_prefill(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
                           const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0, int n_tiles,
-                          void* out, int ldo, float scale, int window, int block, int page_size, int H, int G, cudaStream_t s) {
+                          void* out, int ldo, float scale, int window, int block, int exact_p, int page_size, int H, int G, cudaStream_t s) {
     const size_t smem = (size_t)4 * AM_TILE * HD * 2;
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kern = exact_p ? attn_prefill_mma_kernel<HD, true> : attn_prefill_mma_kernel<HD, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    kp_launch_pdl(attn_prefill_mma_kernel<HD>, dim3(dim3(n_tiles, H)), dim3(128), smem, s, 
+    kp_launch_pdl(kern, dim3(dim3(n_tiles, H)), dim3(128), smem, s, 
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
         (bf16*)out, ldo, scale, window, page_size, H, G, block);
     return kp_launch_status();
@@ -753,8 +806,8 @@ extern "C" {
 // merge of attention_decode.cu afterwards (kp_attention_merge, same chunk size) on the same scratch.
 int kp_attention_split_mma_masked(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
                                   int max_blocks, const int* row_seg, const int* positions, float* scratch, int n_chunks,
-                                  int chunk_keys, float scale, int window, int block, int page_size, int n, int H, int G,
-                                  int hd, void* stream) {
+                                  int chunk_keys, float scale, int window, int block, int exact_p, int page_size, int n, int H,
+                                  int G, int hd, void* stream) {
     if (n <= 0) return 0;
     if (block < 0) return KP_ERR_BAD_ARG;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || H / G > AM_RMAX || page_size < 1 || n_chunks < 1 || n > 65535 ||
@@ -765,7 +818,7 @@ int kp_attention_split_mma_masked(const void* q, int ldq, const void* cache, lon
     cudaStream_t s = (cudaStream_t)stream;
 #define AM_SPLIT(HD, NW)                                                                                          \
     return launch_split<HD, NW>(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, part_acc, part_ml, \
-                                n_chunks, scale, window, block, page_size, n, H, G, s)
+                                n_chunks, scale, window, block, exact_p, page_size, n, H, G, s)
     if (hd == 64) {
         if (chunk_keys == 64) AM_SPLIT(64, 1);
         if (chunk_keys == 128) AM_SPLIT(64, 2);
@@ -781,24 +834,25 @@ int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long 
                            const int* row_seg, const int* positions, float* scratch, int n_chunks, int chunk_keys,
                            float scale, int window, int page_size, int n, int H, int G, int hd, void* stream) {
     return kp_attention_split_mma_masked(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, scratch, n_chunks,
-                                         chunk_keys, scale, window, 0, page_size, n, H, G, hd, stream);
+                                         chunk_keys, scale, window, 0, 0, page_size, n, H, G, hd, stream);
 }
 
 // tile_seg / tile_row0: for each tile of 64 rows its segment and its first row (device arrays, n_tiles long)
-// block: 0, or the size of the blocks of positions beyond whose start a row reads no key.
+// block: 0, or the size of the blocks of positions beyond whose start a row reads no key.  exact_p: 1 takes the
+// softmax weights into the product with V whole (three bfloat16 parts), 0 rounded to bfloat16.
 int kp_attention_prefill_mma_masked(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
                                     const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
-                                    int n_tiles, void* out, int ldo, float scale, int window, int block, int page_size,
-                                    int H, int G, int hd, void* stream) {
+                                    int n_tiles, void* out, int ldo, float scale, int window, int block, int exact_p,
+                                    int page_size, int H, int G, int hd, void* stream) {
     if (n_tiles <= 0) return 0;
     if (block < 0) return KP_ERR_BAD_ARG;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || page_size < 1 || H > 65535 || (ldq & 1) || (ldo & 1))
         return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return launch_prefill<64>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-                                            n_tiles, out, ldo, scale, window, block, page_size, H, G, s);
+                                            n_tiles, out, ldo, scale, window, block, exact_p, page_size, H, G, s);
     return launch_prefill<128>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
-                               out, ldo, scale, window, block, page_size, H, G, s);
+                               out, ldo, scale, window, block, exact_p, page_size, H, G, s);
 }
 
 int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
@@ -806,7 +860,7 @@ int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const in
                              int n_tiles, void* out, int ldo, float scale, int window, int page_size, int H, int G,
                              int hd, void* stream) {
     return kp_attention_prefill_mma_masked(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
-                                           n_tiles, out, ldo, scale, window, 0, page_size, H, G, hd, stream);
+                                           n_tiles, out, ldo, scale, window, 0, 0, page_size, H, G, hd, stream);
 }
 
 

@@ -27,6 +27,7 @@ from ..config.registry import register_architecture
 ARCHITECTURE = "Tizusun"
 DENSE_ACTIVATION = "relu"
 EXPERT_ACTIVATION = "silu"
+SOFTMAX_WEIGHTS = "float32"        # the design computes scores and weights in 32-bit, also where they meet the values
 DEFAULT_MAX_POSITIONS = 131072     # the design itself sets no limit; an optional key ``max_positions`` overrides
 
 
@@ -121,6 +122,7 @@ def _mixer_spec(c: TizusunConfig, m: Dict[str, Any], prefix: str) -> PartSpec:
         {"hidden_size": c.width, "num_heads": int(m["heads"]), "num_kv_heads": int(m["kv_heads"]),
          "head_dim": int(m["dim"]), "qk_norm_eps": c.eps, "scale": float(m["scale"]), "window": None,
          "block": int(mask["size"]) if mask else None, "values": "keys", "gate": "sigmoid",
+         "softmax_weights": SOFTMAX_WEIGHTS,
          "position": position, "bias": False},
         prefix,
         rename={"q_proj.weight": "q", "k_proj.weight": "k", "q_norm.weight": "q.norm", "k_norm.weight": "k.norm",

@@ -533,10 +533,12 @@ def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
                     window: Optional[int], page_size: int, H: int, G: int, hd: int,
-                    block: Optional[int] = None) -> torch.Tensor:
+                    block: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
     """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
     must cover the largest position of the batch; ``scratch`` is float32.
-    ``block``: a row reads no key from before the start of its own block of that many positions."""
+    ``block``: a row reads no key from before the start of its own block of that many positions.
+    ``exact_weights``: the softmax weights enter the product with V whole (the scalar kernel always does so; the
+    tensor-core form then multiplies their three bfloat16 parts one after the other) instead of rounded to bfloat16."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
@@ -553,7 +555,7 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), int(block or 0),
-            page_size, n, H, G, hd, STREAM)
+            int(bool(exact_weights)), page_size, n, H, G, hd, STREAM)
         _run("attention_merge", lib.kp_attention_merge_masked, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
              parts, SPLIT_CHUNK_MMA, int(window or 0), int(block or 0), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
@@ -590,12 +592,14 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
                       seg_pos: torch.Tensor, tile_seg: torch.Tensor, tile_row0: torch.Tensor, out: torch.Tensor,
                       scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int,
                       big_tile_seg: Optional[torch.Tensor] = None, big_tile_row0: Optional[torch.Tensor] = None,
-                      block: Optional[int] = None) -> torch.Tensor:
+                      block: Optional[int] = None, exact_weights: bool = False) -> torch.Tensor:
     """Tensor-core causal attention for segments of many rows.  ``tile_seg`` / ``tile_row0`` list, for every
     tile of 64 consecutive rows of a segment, its segment and its first row; ``big_tile_seg`` /
     ``big_tile_row0`` the same for tiles of 128 rows, the tile that reads the most keys first (with them the
     tcgen05 kernel runs where it takes the sizes).  ``block``: a row reads no key from before the start of its own
-    block of that many positions."""
+    block of that many positions.  ``exact_weights``: the softmax weights enter the product with V whole, as three
+    bfloat16 parts multiplied one after the other (the mma.sync kernel; the tcgen05 kernel, whose weights pass
+    through shared memory as one bfloat16 operand, is then not taken)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(cache, "cache", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
     for t_, nm in ((block_table, "block_table"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (tile_seg, "tile_seg"),
@@ -606,7 +610,7 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         raise KernelError("attention_prefill: shape mismatch")
     if tile_seg.numel() != tile_row0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
-    if big_tile_seg is not None and attention_prefill_tc_ok(q, out, cache, page_size, hd):
+    if big_tile_seg is not None and not exact_weights and attention_prefill_tc_ok(q, out, cache, page_size, hd):
         _need(big_tile_seg, "big_tile_seg", torch.int32); _need(big_tile_row0, "big_tile_row0", torch.int32)
         if big_tile_seg.numel() != big_tile_row0.numel():
             raise KernelError("attention_prefill: tile lists differ in length")
@@ -620,7 +624,7 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma_masked,
         _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
         _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
-        int(window or 0), int(block or 0), page_size, H, G, hd, STREAM)
+        int(window or 0), int(block or 0), int(bool(exact_weights)), page_size, H, G, hd, STREAM)
     return out
 
 

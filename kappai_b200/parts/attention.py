@@ -16,11 +16,15 @@ key from before the start of its own block, blocks being counted from position
 0 of the sequence, whatever the portions a prompt is run in; ``gate`` =
 ``"sigmoid"`` multiplies the concatenated heads, element by element, with
 ``sigmoid(h Wg^T)`` in front of the output matrix (Wg rides in the same product
-as q and k).
+as q and k).  ``softmax_weights`` = ``"float32"`` keeps the softmax weights
+whole where they are multiplied with the values (the general and scalar kernels
+always do; the ``mma.sync`` kernels then take them as three bfloat16 parts, and
+the tcgen05 prompt kernel, which rounds them to one bfloat16 operand, is left
+out); the default ``"operand"`` rounds them to bfloat16 as a matrix operand.
 
 Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
 scale, qk_norm_eps (None: no q/k norm), window (None: all keys), block (None),
-values ("projection" | "keys"), gate (None | "sigmoid"), position (a
+values ("projection" | "keys"), gate (None | "sigmoid"), softmax_weights ("operand" | "float32"), position (a
 ``position`` PartSpec), bias.
 """
 from __future__ import annotations
@@ -109,6 +113,10 @@ class Attention(Part):
         if gate not in (None, "sigmoid"):
             raise ConfigError(f"attention: gate='{gate}' (expected 'sigmoid' or none)")
         self.gated = gate is not None
+        sw = self._p("softmax_weights", "operand")
+        if sw not in ("operand", "float32"):
+            raise ConfigError(f"attention: softmax_weights='{sw}' (expected 'operand' or 'float32')")
+        self.exact_weights = sw == "float32"
         if self.bias and (self.values_are_keys or self.gated):
             raise ConfigError("attention: biases are not combined with values='keys' or a gate")
         if self.H < 1 or self.G < 1 or self.H % self.G:
@@ -207,13 +215,13 @@ class Attention(Part):
                 t0 = tiles.n_short_tiles
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg[t0:],
                                     tiles.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
-                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block)
+                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block, exact_weights=self.exact_weights)
             else:
                 # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
                 big = (None, None) if lead else (tiles.big_tile_seg, tiles.big_tile_row0)
                 K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
                                     tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big,
-                                    block=self.block)
+                                    block=self.block, exact_weights=self.exact_weights)
         else:
             lead = tiles.n_short_rows if tiles is not None else 0
             if lead and self.split_ok:
@@ -243,7 +251,8 @@ class Attention(Part):
                              device=q.device)
             self.env.shared["attn_scratch"] = ws
         K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
-                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block)
+                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block,
+                          self.exact_weights)
 
 
 register_part("mixer", "attention", Attention)

@@ -45,19 +45,19 @@ TIZ_R = {"architecture": "Tizusun", "vocab": 150, "width": 36, "postln_alpha": 3
 ]}
 # S: head size 64 with a block of 100 positions that page borders (64) and key chunks (256) cut
 TIZ_S = {"architecture": "Tizusun", "vocab": 300, "width": 128, "postln_alpha": 2.0, "norm": {"eps": 1e-5}, "layers": [
-    _layer(_attn(4, 1, 64, {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 128}}, 100),
+    _layer(_attn(4, 1, 64, {"base": 10000.0, "dims": 32, "scaling": {"factor": 3.0, "low": 1.5, "high": 6.0, "original": 128}}, 100),
            _MOE(8, 2, 64)),
-    _layer(_attn(4, 1, 64, {"base": 10000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 128}}, 100),
+    _layer(_attn(4, 1, 64, {"base": 10000.0, "dims": 32, "scaling": {"factor": 3.0, "low": 1.5, "high": 6.0, "original": 128}}, 100),
            _MOE(8, 2, 64)),
 ]}
 
 # T: widths at which the decode products stream their weights (K a multiple of 512) and the prompt products run on
 # tcgen05; head size 128 (mma.sync prompt kernel, split-key tensor-core decode), as many kv heads as heads, a block
 # as long as a page, rotation of half a head
-TIZ_T = {"architecture": "Tizusun", "vocab": 500, "width": 512, "postln_alpha": 2.5, "norm": {"eps": 1e-5}, "layers": [
-    _layer(_attn(4, 4, 128, {"base": 50000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
+TIZ_T = {"architecture": "Tizusun", "vocab": 500, "width": 512, "postln_alpha": 2.25, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_attn(4, 4, 128, {"base": 20000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
            _DENSE(1024)),
-    _layer(_attn(4, 4, 128, {"base": 50000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
+    _layer(_attn(4, 4, 128, {"base": 20000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 2.0, "original": 64}}, 64),
            _MOE(4, 2, 128)),
 ]}
 # U: blocks of one position (a token reads itself alone) and of three, two experts of which one, a vocabulary smaller than a warp
