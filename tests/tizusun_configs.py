@@ -67,7 +67,14 @@ TIZ_U = {"architecture": "Tizusun", "vocab": 19, "width": 32, "postln_alpha": 1.
     _layer(_attn(1, 1, 32, None, None), _MOE(2, 2, 40)),
 ]}
 
-CONFIGS = {"P": (TIZ_P, 3), "Q": (TIZ_Q, 4), "R": (TIZ_R, 5), "S": (TIZ_S, 6), "T": (TIZ_T, 7), "U": (TIZ_U, 8)}
+# V: prompts long enough that a step has more than 512 (row, expert) pairs: the experts' products then run as grouped
+# tcgen05 tiles, some experts with several tiles, some with a part of one
+TIZ_V = {"architecture": "Tizusun", "vocab": 400, "width": 256, "postln_alpha": 1.75, "norm": {"eps": 1e-5}, "layers": [
+    _layer(_attn(4, 2, 64, {"base": 10000.0, "dims": 32}, 150), _MOE(8, 2, 72)),
+    _layer(_attn(4, 2, 64, {"base": 10000.0, "dims": 32}, 150), _MOE(5, 3, 136)),
+]}
+
+CONFIGS = {"P": (TIZ_P, 3), "Q": (TIZ_Q, 4), "R": (TIZ_R, 5), "S": (TIZ_S, 6), "T": (TIZ_T, 7), "U": (TIZ_U, 8), "V": (TIZ_V, 9)}
 
 
 def tensor_shapes(cfg):
