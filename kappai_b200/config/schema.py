@@ -133,7 +133,8 @@ class PartSpec:
 class LayerSpec:
     """A block: the arrangement (``block``, with its constants in
     ``block_params``) of a mixer, a feed-forward and the norms it needs.  Chosen
-    layer by layer."""
+    layer by layer.  ``side`` (category ``side``): something that changes the
+    residual at the layer's end, behind the feed-forward."""
 
     mixer: PartSpec
     ffn: Optional[PartSpec]
@@ -141,6 +142,7 @@ class LayerSpec:
     ffn_norm: Optional[PartSpec]
     block: str = "prenorm_residual"
     block_params: Dict[str, Any] = field(default_factory=dict)
+    side: Optional[PartSpec] = None
 
 
 @dataclass
@@ -148,10 +150,13 @@ class ScheduleEntry:
     """One run of a layer.  ``layer`` indexes :attr:`ModelSpec.layers` (a layer
     may be named by several entries: its weights are then shared and every entry
     gets a cache of its own).  ``cache_of`` names an earlier schedule entry whose
-    cache this run reads instead of keeping one (it then writes nothing)."""
+    cache this run reads instead of keeping one (it then writes nothing).
+    ``enter``: the model's ``entry`` part runs on the residual right before this
+    run (the head of a pass over a stretch of layers)."""
 
     layer: int
     cache_of: Optional[int] = None
+    enter: bool = False
 
 
 @dataclass
@@ -166,10 +171,16 @@ class ModelSpec:
     final_norm: Optional[PartSpec]
     head: PartSpec
     eos_token_id: Optional[int] = None
+    entry: Optional[PartSpec] = None           # category ``entry``: runs in front of schedule entries marked ``enter``
+    token_table: Optional[PartSpec] = None     # a second table by token id that the layers' ``side`` parts read
 
     def validate(self) -> None:
         if self.hidden_size < 1 or self.vocab_size < 1:
             raise ConfigError("hidden_size and vocab_size must be positive")
+        if any(e.enter for e in self.schedule) and self.entry is None:
+            raise ConfigError("a schedule entry is marked 'enter' but the model has no entry part")
+        if any(ls.side is not None for ls in self.layers) and self.token_table is None:
+            raise ConfigError("a layer has a side part but the model has no token table")
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.layers)):
                 raise ConfigError(f"schedule[{i}] names layer {e.layer}, model has {len(self.layers)}")

@@ -44,10 +44,12 @@ __device__ __forceinline__ float kp_act_rt(int act, float g) {
     return act == KP_ACT_RELU ? kp_act<KP_ACT_RELU>(g) : (act == KP_ACT_GELU_TANH ? kp_act<KP_ACT_GELU_TANH>(g) : kp_act<KP_ACT_SILU>(g));
 }
 
-// For the epilogues of the products (a cheap choice at run time: silu unless relu is asked for).  A launcher's
+// For the epilogues of the products (a choice at run time: silu unless another is asked for).  A launcher's
 // `epi` argument carries the activation of its gated epilogue in bits 8 and up.
-__device__ __forceinline__ float kp_act_silu_or_relu(int act, float g) {
-    return act == KP_ACT_RELU ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
+__device__ __forceinline__ float kp_act_epilogue(int act, float g) {
+    if (act == KP_ACT_RELU) return fmaxf(g, 0.f);
+    if (act == KP_ACT_GELU_TANH) return kp_act<KP_ACT_GELU_TANH>(g);
+    return g / (1.0f + expf(-g));
 }
 #define KP_EPI_ACT(epi) (((epi) >> 8) & 0xff)
 #define KP_EPI_KIND(epi) ((epi) & 0xff)

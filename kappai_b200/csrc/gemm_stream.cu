@@ -318,7 +318,7 @@ gemm_stream_kernel(const StreamArgs p) {
                 if (p.bias) u += p.bias[p.ff + n];
                 // gate and up are rounded to the storage type before the activation, as the unfused path stores them
                 const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-                ((bf16*)p.C)[o] = from_f32<bf16>(kp_act_silu_or_relu(p.act, gq) * uq);
+                ((bf16*)p.C)[o] = from_f32<bf16>(kp_act_epilogue(p.act, gq) * uq);
             } else if (EPI == EPI_STORE) {
                 ((bf16*)p.C)[o] = from_f32<bf16>(v);
             } else if (EPI == EPI_STORE_F32) {
@@ -425,7 +425,7 @@ int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* 
     StreamArgs a = {};
     a.act = KP_EPI_ACT(epi);
     epi = KP_EPI_KIND(epi);
-    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU) return KP_ERR_UNSUPPORTED;
+    if (a.act != KP_ACT_SILU && a.act != KP_ACT_RELU && a.act != KP_ACT_GELU_TANH) return KP_ERR_UNSUPPORTED;
     int st = check_common(a, M, N, K, ldw, W, epi);
     if (st) return st;
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;

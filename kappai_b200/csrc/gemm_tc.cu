@@ -99,7 +99,7 @@ __device__ __forceinline__ void tc_finish(const TcArgs& p, int n_lim, const floa
             if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
             // gate and up are rounded to the storage type first, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-            x = kp_act_silu_or_relu(p.act, gq) * uq;
+            x = kp_act_epilogue(p.act, gq) * uq;
         }
         v[j] = x;
     }
@@ -526,7 +526,7 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
     if (M <= 0 || N <= 0) return 0;
     const int act = KP_EPI_ACT(epi);
     epi = KP_EPI_KIND(epi);
-    if (act != KP_ACT_SILU && act != KP_ACT_RELU) return KP_ERR_UNSUPPORTED;
+    if (act != KP_ACT_SILU && act != KP_ACT_RELU && act != KP_ACT_GELU_TANH) return KP_ERR_UNSUPPORTED;
     if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
     TcArgs a = {};

@@ -5,6 +5,11 @@
 //   chosen(r) = the `top` largest z[r, :] (ties: the lower index), weights = softmax over the chosen logits only
 //   out[r, :] += sum_j weight_j * Wd_e (act(Wg_e h_r) * (Wu_e h_r)),  e = chosen_j(r), j in order
 //
+// A second way of choosing (`mode` 1): scores s = softmax(z) over ALL router outputs; the `top` largest s + b are
+// chosen (b: a correction that takes part in the choice only), and the weights are the chosen s themselves times a
+// constant, not renormalised.  The last `n_identity` router outputs may stand for experts without weights that
+// return their input: their pairs get places in the layout but no tiles, and the combine adds weight * h for them.
+//
 // Which rows meet which expert is known on the device only, so the work is laid out there too and nothing
 // comes back to the host (a step with this layer can be captured in a CUDA graph):
 //   moe_route:  one warp a row picks the experts and their weights;
@@ -24,17 +29,26 @@
 #define MOE_SORT_THREADS 1024
 
 // ------------------------------------------------------------------------------------------------ route
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* __restrict__ idx_out,
-                 float* __restrict__ w_out) {
-    kp_pdl_begin();
-    extern __shared__ float route_sm[];                         // [warps][E]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (r >= n) return;
-    float* z = route_sm + (size_t)warp * E;
-    for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)r * E + e];
-    __syncwarp();
+// One warp chooses for one row.  z [E]: the row's router logits in shared memory (mode 0: bias already added); they
+// are overwritten.  s [E]: room for the scores of mode 1.
+__device__ __forceinline__ void moe_choose(float* z, float* s, int E, int top, int mode, const float* __restrict__ bias,
+                                           float wscale, int* __restrict__ idx_out, float* __restrict__ w_out) {
+    const int lane = threadIdx.x & 31;
+    if (mode == 1) {
+        // scores over all outputs; the choice runs over score + correction, the weight is the score
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - m); s[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) {
+            const float sc = s[e] / sum;
+            s[e] = sc;
+            z[e] = sc + (bias ? bias[e] : 0.f);
+        }
+        __syncwarp();
+    }
     float my_z = -INFINITY;
     int my_e = 0;
     for (int j = 0; j < top; j++) {
@@ -55,13 +69,34 @@ moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* _
         if (lane == 0) z[bi] = -INFINITY;
         __syncwarp();
     }
+    if (mode == 1) {
+        if (lane < top) {
+            idx_out[lane] = my_e;
+            w_out[lane] = s[my_e] * wscale;
+        }
+        return;
+    }
     const float m = __shfl_sync(0xffffffffu, my_z, 0);
     const float p = lane < top ? expf(my_z - m) : 0.f;
     const float sum = warp_sum(p);
     if (lane < top) {
-        idx_out[(size_t)r * top + lane] = my_e;
-        w_out[(size_t)r * top + lane] = p / sum;
+        idx_out[lane] = my_e;
+        w_out[lane] = p / sum;
     }
+}
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n, int E, int top, int mode,
+                 float wscale, int* __restrict__ idx_out, float* __restrict__ w_out) {
+    kp_pdl_begin();
+    extern __shared__ float route_sm[];                         // [warps][2 E]: logits, scores
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= n) return;
+    float* z = route_sm + (size_t)warp * 2 * E;
+    for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)r * E + e] + (mode == 0 && bias ? bias[e] : 0.f);
+    __syncwarp();
+    moe_choose(z, z + E, E, top, mode, bias, wscale, idx_out + (size_t)r * top, w_out + (size_t)r * top);
 }
 
 // The router as one kernel: logits z = h Wr^T + b in float32 (h is widened from its storage type; a row's
@@ -73,9 +108,9 @@ moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int* _
 template <typename T, int RB>
 __global__ void __launch_bounds__(256)
 moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr, const float* __restrict__ bias, int n,
-                  int E, int d, int top, int* __restrict__ idx_out, float* __restrict__ w_out) {
+                  int E, int d, int top, int mode, float wscale, int* __restrict__ idx_out, float* __restrict__ w_out) {
     kp_pdl_begin();
-    extern __shared__ __align__(16) float router_sm[];          // [RB][d] rows, [RB][E] logits
+    extern __shared__ __align__(16) float router_sm[];          // [RB][d] rows, [RB][2 E] logits and scores
     float* hs = router_sm;
     float* zs = router_sm + (size_t)RB * d;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -117,39 +152,13 @@ moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr
 #pragma unroll
             for (int r = 0; r < RB; r++) {
                 const float v = warp_sum(acc[j][r]);
-                if (lane == 0 && has[j]) zs[(size_t)r * E + e0 + 8 * j] = v + (bias ? bias[e0 + 8 * j] : 0.f);
+                if (lane == 0 && has[j]) zs[(size_t)r * 2 * E + e0 + 8 * j] = v + (mode == 0 && bias ? bias[e0 + 8 * j] : 0.f);
             }
     }
     __syncthreads();
     if (warp >= nr) return;
-    float* z = zs + (size_t)warp * E;                            // warp r chooses for row r
-    float my_z = -INFINITY;
-    int my_e = 0;
-    for (int j = 0; j < top; j++) {
-        float best = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > best) { best = v; bi = e; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-        }
-        if (bi == 0x7fffffff) bi = 0;
-        if (lane == j) { my_z = best; my_e = bi; }
-        if (lane == 0) z[bi] = -INFINITY;
-        __syncwarp();
-    }
-    const float m = __shfl_sync(0xffffffffu, my_z, 0);
-    const float p = lane < top ? expf(my_z - m) : 0.f;
-    const float sum = warp_sum(p);
-    if (lane < top) {
-        idx_out[(size_t)(row0 + warp) * top + lane] = my_e;
-        w_out[(size_t)(row0 + warp) * top + lane] = p / sum;
-    }
+    float* z = zs + (size_t)warp * 2 * E;                        // warp r chooses for row r
+    moe_choose(z, z + E, E, top, mode, bias, wscale, idx_out + (size_t)(row0 + warp) * top, w_out + (size_t)(row0 + warp) * top);
 }
 
 // ------------------------------------------------------------------------------------------------- sort
@@ -157,7 +166,7 @@ moe_router_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wr
 // of MOE_BM places (tile_start[E] = all tiles), big_start the same for tiles of MOE_BIG places.
 // perm[place] = pair (row * top + j); inv[pair] = place.
 __global__ void __launch_bounds__(MOE_SORT_THREADS)
-moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ offsets, int* __restrict__ tile_start,
+moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int E_real, int* __restrict__ offsets, int* __restrict__ tile_start,
                 int* __restrict__ big_start, int* __restrict__ perm, int* __restrict__ inv) {
     kp_pdl_begin();
     extern __shared__ int sort_sm[];                            // [E] counts, [E] cursors, [E + 1] offsets
@@ -173,8 +182,10 @@ moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict
         for (int e = 0; e < E; e++) {
             off[e] = o; offsets[e] = o; tile_start[e] = t; big_start[e] = tb;
             o += cnt[e];
-            t += (cnt[e] + MOE_BM - 1) / MOE_BM;
-            tb += (cnt[e] + MOE_BIG - 1) / MOE_BIG;
+            if (e < E_real) {                                   // (experts without weights have places but no tiles)
+                t += (cnt[e] + MOE_BM - 1) / MOE_BM;
+                tb += (cnt[e] + MOE_BIG - 1) / MOE_BIG;
+            }
         }
         off[E] = o; offsets[E] = o; tile_start[E] = t; big_start[E] = tb;
     }
@@ -674,6 +685,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
+// The same where the experts from `E_real` on return their input: such a pair adds weight * h[r].
+template <typename T>
+__global__ void moe_combine_identity_kernel(const float* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ w,
+                                            const int* __restrict__ idx, const T* __restrict__ h, int ldh, int E_real,
+                                            float* __restrict__ out, int n, int d, int top) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * d;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / d, c = i % d;
+        float s = 0.f;
+        for (int j = 0; j < top; j++) {
+            const float v = idx[r * top + j] >= E_real ? to_f32(h[r * ldh + c]) : y[(size_t)inv[r * top + j] * d + c];
+            s = fmaf(w[r * top + j], v, s);
+        }
+        out[i] += s;
+    }
+}
+
 static long long g_moe_tc_min_pairs = 512;      // (row, choice) pairs from which the tcgen05 tiles are taken
 
 extern "C" {
@@ -691,13 +720,21 @@ int kp_moe_max_tiles(int n, int E, int top) {
 }
 
 // logits [n, E] float32 -> idx [n, top], weights [n, top], and the layout (see kp_moe_layout_ints).
-int kp_moe_route(const float* logits, int n, int E, int top, int* idx, float* weights, int* layout, void* stream) {
+// mode 0: the largest logits (+ bias), weights = softmax over the chosen; mode 1: scores = softmax over all, the largest
+// score + bias chosen, weights = score * wscale.  The last n_identity of the E outputs are experts without weights.
+int kp_moe_route(const float* logits, const float* bias, int n, int E, int top, int mode, float wscale, int n_identity,
+                 int* idx, float* weights, int* layout, void* stream) {
     if (n <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return KP_ERR_UNSUPPORTED;
-    const size_t route_sm = (size_t)8 * E * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
-    if (route_sm > 48 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;            // (E <= 1536)
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 1 || n_identity < 0 || n_identity >= E)
+        return KP_ERR_UNSUPPORTED;
+    const size_t route_sm = (size_t)8 * 2 * E * sizeof(float), sort_sm = ((size_t)3 * E + 1) * sizeof(int);
+    if (route_sm > 96 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;            // (E <= 1536)
     cudaStream_t s = (cudaStream_t)stream;
-    kp_launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), route_sm, s, logits, n, E, top, idx, weights);
+    if (route_sm > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_sm);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kp_launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), route_sm, s, logits, bias, n, E, top, mode, wscale, idx, weights);
     cudaError_t e0 = cudaGetLastError();
     if (e0 != cudaSuccess) return (int)e0;
     int* offsets = layout;
@@ -705,22 +742,23 @@ int kp_moe_route(const float* logits, int n, int E, int top, int* idx, float* we
     int* big_start = tile_start + (E + 1);
     int* perm = big_start + (E + 1);
     int* inv = perm + (size_t)n * top;
-    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, offsets, tile_start,
-                  big_start, perm, inv);
+    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, E - n_identity, offsets,
+                  tile_start, big_start, perm, inv);
     return kp_launch_status();
 }
 
 // The router in one go: rows h [n, d] (storage type `dtype`), Wr [E, d] and b [E] (or null) in float32 -> idx, weights
 // and the layout.  KP_ERR_UNSUPPORTED where the rows do not fit the kernel's shared memory or alignment (the caller
 // then computes the logits with a matrix product and calls kp_moe_route).
-int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, int n, int E, int d, int top, int* idx,
-                  float* weights, int* layout, int dtype, void* stream) {
+int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, int n, int E, int d, int top, int mode,
+                  float wscale, int n_identity, int* idx, float* weights, int* layout, int dtype, void* stream) {
     if (n <= 0) return 0;
-    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP) return KP_ERR_UNSUPPORTED;
+    if (E < 1 || top < 1 || top > E || top > MOE_MAX_TOP || mode < 0 || mode > 1 || n_identity < 0 || n_identity >= E)
+        return KP_ERR_UNSUPPORTED;
     const size_t sort_sm = ((size_t)3 * E + 1) * sizeof(int);
     // eight rows a block where there are many and they fit shared memory, else one
-    const int rb = (n > 64 && ((size_t)8 * (d + E)) * sizeof(float) <= 200 * 1024) ? 8 : 1;
-    const size_t sm = ((size_t)rb * d + (size_t)rb * E) * sizeof(float);
+    const int rb = (n > 64 && ((size_t)8 * (d + 2 * E)) * sizeof(float) <= 200 * 1024) ? 8 : 1;
+    const size_t sm = ((size_t)rb * d + (size_t)rb * 2 * E) * sizeof(float);
     if ((d & 3) || ((uintptr_t)wr & 15) || sm > 200 * 1024 || sort_sm > 48 * 1024) return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
 #define MOE_ROUTER_LAUNCH(T, RB)                                                                                          \
@@ -730,7 +768,7 @@ int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, in
             if (e != cudaSuccess) return (int)e;                                                                          \
         }                                                                                                                 \
         kp_launch_pdl(moe_router_kernel<T, RB>, dim3((n + RB - 1) / RB), dim3(256), sm, s, (const T*)h, ldh, wr, bias, n, E, d, \
-                      top, idx, weights);                                                                                 \
+                      top, mode, wscale, idx, weights);                                                                   \
     } while (0)
     KP_DISPATCH_DTYPE(dtype, T, { if (rb == 8) MOE_ROUTER_LAUNCH(T, 8); else MOE_ROUTER_LAUNCH(T, 1); });
 #undef MOE_ROUTER_LAUNCH
@@ -741,18 +779,22 @@ int kp_moe_router(const void* h, int ldh, const float* wr, const float* bias, in
     int* big_start = tile_start + (E + 1);
     int* perm = big_start + (E + 1);
     int* inv = perm + (size_t)n * top;
-    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, offsets, tile_start,
-                  big_start, perm, inv);
+    kp_launch_pdl(moe_sort_kernel, dim3(1), dim3(MOE_SORT_THREADS), sort_sm, s, (const int*)idx, n * top, E, E - n_identity, offsets,
+                  tile_start, big_start, perm, inv);
     return kp_launch_status();
 }
 
 // h [n, d] -> act [n top, ff] (by place) -> y [n top, d] float32 (by place) -> out [n, d] += weighted sum.
 // hs: scratch [n top, d] in the storage type for the tcgen05 path (null: that path is not taken).
+// E counts all router outputs; the last n_identity of them are experts without weights (w_gu and w_down hold
+// E - n_identity experts), for which `idx` [n, top] (the chosen experts) must be given.
 int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down, const int* layout, const float* weights,
                    void* act, float* y, float* out, void* hs, int n, int E, int top, int d, int ff, int act_kind, int dtype,
-                   void* stream) {
+                   int n_identity, const int* idx, void* stream) {
     if (n <= 0) return 0;
     if (E < 1 || top < 1 || d < 1 || ff < 1 || act_kind < 0 || act_kind > KP_ACT_GELU_TANH) return KP_ERR_BAD_ARG;
+    if (n_identity < 0 || n_identity >= E || (n_identity > 0 && idx == nullptr)) return KP_ERR_BAD_ARG;
+    const int E_real = E - n_identity;
     const int max_tiles = kp_moe_max_tiles(n, E, top);
     if (max_tiles > 65535) return KP_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -767,13 +809,13 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
     const long long pairs = (long long)n * top;
     const long long big_tiles = pairs / MOE_BIG + (pairs < E ? pairs : E);
     if (tc && hs != nullptr && pairs >= g_moe_tc_min_pairs && big_tiles <= 65535 && !((uintptr_t)hs & 15) &&
-        (long long)E * 2 * ff < 2147483647LL && (long long)E * d < 2147483647LL) {
+        (long long)E_real * 2 * ff < 2147483647LL && (long long)E_real * d < 2147483647LL) {
         // many rows an expert: the tcgen05 tiles
         alignas(64) CUtensorMap ta1, tw1, ta2, tw2;
         int st = kp_make_map_bf16_2d(&ta1, hs, (unsigned long long)pairs, d, d, MT_BK, MOE_BIG);
-        if (!st) st = kp_make_map_bf16_2d(&tw1, w_gu, (unsigned long long)E * 2 * ff, d, d, MT_BK, MT_BN / 2);
+        if (!st) st = kp_make_map_bf16_2d(&tw1, w_gu, (unsigned long long)E_real * 2 * ff, d, d, MT_BK, MT_BN / 2);
         if (!st) st = kp_make_map_bf16_2d(&ta2, act, (unsigned long long)pairs, ff, ff, MT_BK, MOE_BIG);
-        if (!st) st = kp_make_map_bf16_2d(&tw2, w_down, (unsigned long long)E * d, ff, ff, MT_BK, MT_BN);
+        if (!st) st = kp_make_map_bf16_2d(&tw2, w_down, (unsigned long long)E_real * d, ff, ff, MT_BK, MT_BN);
         if (st) return st;
         const size_t smem = (size_t)MT_STAGES * (MT_A_BYTES + MT_B_BYTES) + (2 * MT_STAGES + 1) * 8 + 16 + 1024;
         static bool ready = false;
@@ -812,6 +854,11 @@ int kp_moe_experts(const void* h, int ldh, const void* w_gu, const void* w_down,
     }
     size_t g = ((size_t)n * d + 255) / 256;
     if (g > 148 * 16) g = 148 * 16;
+    if (n_identity > 0) {
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(moe_combine_identity_kernel<T>, dim3((unsigned)g), dim3(256), 0, s, (const float*)y,
+                                                   inv, weights, idx, (const T*)h, ldh, E_real, out, n, d, top)));
+        return kp_launch_status();
+    }
     kp_launch_pdl(moe_combine_kernel, dim3((unsigned)g), dim3(256), 0, s, (const float*)y, inv, weights, out, n, d, top);
     return kp_launch_status();
 }

@@ -3,14 +3,21 @@
 #include "common.cuh"
 
 // x[r,:] = float(table[ids[r],:])            (src/backend/cpu/common.c:1774-1782)
-// `scale` multiplies the row (1.0 = none; the architecture decides).
+// `scale` multiplies the row (1.0 = none; the architecture decides).  With a table of learned position vectors
+// (`pos_table`, rows by position) the row of the token's position is added, unscaled.
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                  float* __restrict__ x, int d, float scale) {
+                                  float* __restrict__ x, int d, float scale, const T* __restrict__ pos_table,
+                                  const int* __restrict__ positions) {
     kp_pdl_begin();
     const int r = blockIdx.x;
     const T* src = table + (size_t)ids[r] * d;
     float* dst = x + (size_t)r * d;
+    if (pos_table != nullptr) {
+        const T* ps = pos_table + (size_t)positions[r] * d;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = fmaf(to_f32(src[i]), scale, to_f32(ps[i]));
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_f32(src[i]) * scale;
 }
 
@@ -294,6 +301,99 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
     }
 }
 
+
+// RMS norm of one or two column stretches of rows in the storage type: out_s[r, :] = norm(in[r, c_s : c_s + w_s]) * wt_s
+// (float32 statistics).  For latents that leave one product side by side and are normed each on its own.
+struct ColNorm { int col, width, ld_out; const float* weight; void* out; };
+template <typename T>
+__global__ void __launch_bounds__(128)
+rmsnorm_cols_kernel(const T* __restrict__ in, int ld, ColNorm a, ColNorm b, float eps) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const ColNorm c = blockIdx.y == 0 ? a : b;
+    const int r = blockIdx.x;
+    const T* src = in + (size_t)r * ld + c.col;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < c.width; i += blockDim.x) {
+        const float v = to_f32(src[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)c.width + eps);
+    T* dst = (T*)c.out + (size_t)r * c.ld_out;
+    for (int i = threadIdx.x; i < c.width; i += blockDim.x) dst[i] = from_f32<T>((to_f32(src[i]) * scale) * c.weight[i]);
+}
+
+// out[r, :] = norm(o[r, :]) * w * sigmoid(g[r, :]): the RMS norm of float32 rows (all heads of a mixer's output
+// together) and the output gate in one pass; `g` is columns of a wider row in the storage type.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_gate_rows_kernel(const float* __restrict__ o, const float* __restrict__ w, const T* __restrict__ g, int ldg,
+                      T* __restrict__ out, int ldo, int d, float eps) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* src = o + (size_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float z = to_f32(g[(size_t)r * ldg + i]);
+        out[(size_t)r * ldo + i] = from_f32<T>(((src[i] * scale) * w[i]) * (1.0f / (1.0f + expf(-z))));
+    }
+}
+
+// out[r, c] = act(gate[r, c]) * table[ids[r], col0 + c]: a gate on a stretch of a second token table's row.
+template <typename T>
+__global__ void token_gate_kernel(const T* __restrict__ gate, int ldg, const T* __restrict__ table, int ldt, int col0,
+                                  const int* __restrict__ ids, T* __restrict__ out, int n, int dim, int act_kind) {
+    kp_pdl_begin();
+    const size_t total = (size_t)n * dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / dim, c = i % dim;
+        const float z = to_f32(gate[r * ldg + c]);
+        const float e = to_f32(table[(size_t)ids[r] * ldt + col0 + c]);
+        out[i] = from_f32<T>(kp_act_rt(act_kind, z) * e);
+    }
+}
+
+// x[r, :] += norm(y[r, :]) * w for float32 rows: a branch that is normed before it joins the residual.
+__global__ void __launch_bounds__(256)
+rmsnorm_add_rows_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x, int d, float eps) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* src = y + (size_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = src[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) x[(size_t)r * d + i] += (src[i] * scale) * w[i];
+}
+
+// out[r, :] += sigmoid(h[r, :] . wg) * y[r, :]: a branch weighed by one gate a row, the gate's logit computed here
+// (float32 sum in a fixed order, h widened from its storage type).
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_gate_add_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ wg, const float* __restrict__ y,
+                    float* __restrict__ out, int d) {
+    kp_pdl_begin();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) s = fmaf(to_f32(h[(size_t)r * ldh + i]), wg[i], s);
+    s = block_sum(s, red);
+    const float gate = 1.0f / (1.0f + expf(-s));
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)r * d + i] = fmaf(gate, y[(size_t)r * d + i], out[(size_t)r * d + i]);
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
     kp_pdl_begin();
@@ -345,9 +445,13 @@ __global__ void gather_status_kernel(const unsigned long long* __restrict__ addr
 
 extern "C" {
 
-int kp_embed_rows(const void* table, const int* ids, float* x, int n, int d, float scale, int dtype, void* stream) {
+// pos_table / positions: both given or both null.
+int kp_embed_rows(const void* table, const int* ids, float* x, int n, int d, float scale, const void* pos_table,
+                  const int* positions, int dtype, void* stream) {
     if (n <= 0) return 0;
-    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(embed_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, d, scale)));
+    if ((pos_table == nullptr) != (positions == nullptr)) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(embed_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, d, scale,
+                                               (const T*)pos_table, positions)));
     return kp_launch_status();
 }
 
@@ -416,6 +520,52 @@ int kp_sigmoid_gate(void* o, int ldo, const void* g, int ldg, int n, int cols, i
     const int gr = grid_for((size_t)n * cols, 256);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(sigmoid_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (T*)o, ldo,
                                                (const T*)g, ldg, n, cols)));
+    return kp_launch_status();
+}
+
+
+// One or two column stretches of `in` [n, ld] normed each on its own (width1 = 0: one stretch only).
+int kp_rmsnorm_cols(const void* in, int ld, int n, float eps, int col0, int width0, const float* w0, void* out0, int ldo0,
+                    int col1, int width1, const float* w1, void* out1, int ldo1, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (width0 < 1 || width1 < 0 || col0 < 0 || col1 < 0) return KP_ERR_BAD_ARG;
+    const ColNorm a = {col0, width0, ldo0, w0, out0}, b = {col1, width1, ldo1, w1, out1};
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_cols_kernel<T>, dim3(n, width1 > 0 ? 2 : 1), dim3(128), 0, (cudaStream_t)stream,
+                                               (const T*)in, ld, a, b, eps)));
+    return kp_launch_status();
+}
+
+int kp_norm_gate_rows(const float* o, const float* w, const void* g, int ldg, void* out, int ldo, int n, int d, float eps,
+                      int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(norm_gate_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, o, w,
+                                               (const T*)g, ldg, (T*)out, ldo, d, eps)));
+    return kp_launch_status();
+}
+
+int kp_token_gate(const void* gate, int ldg, const void* table, int ldt, int col0, const int* ids, void* out, int n, int dim,
+                  int act_kind, int dtype, void* stream) {
+    if (n <= 0 || dim <= 0) return 0;
+    if (act_kind < 0 || act_kind > KP_ACT_GELU_TANH || col0 < 0) return KP_ERR_BAD_ARG;
+    const int gr = grid_for((size_t)n * dim, 256);
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(token_gate_kernel<T>, dim3(gr), dim3(256), 0, (cudaStream_t)stream, (const T*)gate,
+                                               ldg, (const T*)table, ldt, col0, ids, (T*)out, n, dim, act_kind)));
+    return kp_launch_status();
+}
+
+int kp_rmsnorm_add_rows(const float* y, const float* w, float* x, int n, int d, float eps, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1) return KP_ERR_BAD_ARG;
+    kp_launch_pdl(rmsnorm_add_rows_kernel, dim3(n), dim3(256), 0, (cudaStream_t)stream, y, w, x, d, eps);
+    return kp_launch_status();
+}
+
+int kp_row_gate_add(const void* h, int ldh, const float* wg, const float* y, float* out, int n, int d, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d < 1) return KP_ERR_BAD_ARG;
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(row_gate_add_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)h, ldh,
+                                               wg, y, out, d)));
     return kp_launch_status();
 }
 

@@ -31,14 +31,18 @@ class Model:
             ffn = self._make("feed_forward", ls.ffn) if ls.ffn is not None else None
             n1 = self._make("norm", ls.mixer_norm) if ls.mixer_norm is not None else None
             n2 = self._make("norm", ls.ffn_norm) if ls.ffn_norm is not None else None
+            side = self._make("side", ls.side) if ls.side is not None else None
             block = make_part("block", PartSpec(ls.block, dict(ls.block_params)), env)
-            self.blocks.append(block.assemble(mixer, ffn, n1, n2))
+            # (an arrangement registered from outside may not know of side parts: it is asked only where there is one)
+            self.blocks.append(block.assemble(mixer, ffn, n1, n2, side) if side is not None else block.assemble(mixer, ffn, n1, n2))
         self.final_norm = self._make("norm", spec.final_norm) if spec.final_norm is not None else None
         self.head = self._make("head", spec.head)
         self.schedule = list(spec.schedule)
-        parts = [self.embedding, self.final_norm, self.head]
+        self.entry = self._make("entry", spec.entry) if spec.entry is not None else None
+        self.token_table = self._make("embedding", spec.token_table) if spec.token_table is not None else None
+        parts = [self.embedding, self.final_norm, self.head, self.entry, self.token_table]
         for b in self.blocks:
-            parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm]
+            parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm, getattr(b, "side", None)]
         # a decode step may be captured in a CUDA graph only if every part reads its tables from the device
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts if p is not None)
         # parts that build tables of their own for every step, one builder per key
@@ -73,6 +77,10 @@ class Model:
             part.bind(w)
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding)
+        if self.token_table is not None:
+            for b in self.blocks:
+                if getattr(b, "side", None) is not None:
+                    b.side.attach(self.token_table)
 
     # -- caches
     def cache_specs(self) -> List[Optional[object]]:
@@ -91,10 +99,24 @@ class Model:
         logits [n_out, vocab] of the wanted rows (None if none are wanted).
         ``observer(where, x)``, if given, is shown the float32 residual behind
         the embedding (where = -1) and behind every schedule entry (its index)."""
-        x = self.embedding.forward(ctx.token_ids)
+        if getattr(self.embedding, "pos_weight", None) is not None:
+            x = self.embedding.forward(ctx.token_ids, ctx.positions)
+        else:
+            x = self.embedding.forward(ctx.token_ids)
         if observer is not None:
             observer(-1, x)
+        h0 = None
+        if self.entry is not None:
+            # the embedding output as the entry part's second operand, kept for every pass
+            from ..ops import kernels as K
+            h0 = torch.empty(x.shape, dtype=self.env.dtype, device=x.device)
+            if self.env.dtype == torch.float32:
+                K.scale_cast(x, None, h0, 1.0)
+            else:
+                K.cast(x, h0)
         for i, e in enumerate(self.schedule):
+            if e.enter:
+                x = self.entry.forward(x, h0)
             self.blocks[e.layer].forward(x, ctx, cache_views[i])
             if observer is not None:
                 observer(i, x)

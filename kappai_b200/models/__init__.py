@@ -1,3 +1,4 @@
 """Built-in architectures.  Importing this package registers them."""
 from . import lfm2  # noqa: F401
 from . import tizusun  # noqa: F401
+from . import vekuzen  # noqa: F401

@@ -262,14 +262,20 @@ def step_tables(src_pinned: torch.Tensor, dst: torch.Tensor, tokens: Optional[to
          _ptr(tokens), tok_off, n_tok, STREAM)
 
 
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+               pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = table[ids[r]] * scale (+ pos_table[positions[r]], a table of learned position vectors)."""
     _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
     n, d = out.shape
     if table.shape[1] != d or ids.numel() != n:
         raise KernelError("embed_rows: shape mismatch")
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype); _need(positions, "positions", torch.int32)
+        if pos_table.shape[1] != d or positions.numel() != n:
+            raise KernelError("embed_rows: position table shape mismatch")
     lib = load_library("rowwise")
     _run("embed_rows", lib.kp_embed_rows, _ptr(table), _ptr(ids), _ptr(out), n, d, ctypes.c_float(scale),
-                             dtype_code(table.dtype), STREAM)
+         _ptr(pos_table), _ptr(positions if pos_table is not None else None), dtype_code(table.dtype), STREAM)
     return out
 
 
@@ -356,6 +362,74 @@ def sigmoid_gate(o: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
     _run("sigmoid_gate", load_library("rowwise").kp_sigmoid_gate, _ptr(o), _rows_2d(o, "o"), _ptr(g), _rows_2d(g, "g"),
          o.shape[0], o.shape[1], dtype_code(o.dtype), STREAM)
     return o
+
+
+def rmsnorm_cols(x: torch.Tensor, stretches, eps: float) -> None:
+    """RMS norm of one or two column stretches of the rows of ``x`` (storage type), each on its own:
+    ``stretches`` = [(first column, weight float32 [width], out [n, width] in x's type), ...]."""
+    _need(x, "x", contiguous=False)
+    if not 1 <= len(stretches) <= 2:
+        raise KernelError("rmsnorm_cols: one or two stretches")
+    n = x.shape[0]
+    args = []
+    for col, w, out in stretches:
+        _need(w, "weight", torch.float32); _need(out, "out", x.dtype, contiguous=False)
+        width = w.numel()
+        if col < 0 or col + width > x.shape[1] or tuple(out.shape) != (n, width):
+            raise KernelError("rmsnorm_cols: shape mismatch")
+        args += [int(col), width, _ptr(w), _ptr(out), _rows_2d(out, "out")]
+    if len(stretches) == 1:
+        args += [0, 0, _ptr(None), _ptr(None), 0]
+    _run("rmsnorm_cols", load_library("rowwise").kp_rmsnorm_cols, _ptr(x), _rows_2d(x, "x"), n, ctypes.c_float(eps), *args,
+         dtype_code(x.dtype), STREAM)
+
+
+def norm_gate_rows(o: torch.Tensor, w: torch.Tensor, g: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = rmsnorm(o) * w * sigmoid(g): float32 rows ``o`` normed whole, gated by columns ``g`` of a wider row."""
+    _need(o, "o", torch.float32); _need(w, "w", torch.float32); _need(g, "g", contiguous=False)
+    _need(out, "out", g.dtype, contiguous=False)
+    n, d = o.shape
+    if w.numel() != d or tuple(g.shape) != (n, d) or tuple(out.shape) != (n, d):
+        raise KernelError("norm_gate_rows: shape mismatch")
+    _run("norm_gate_rows", load_library("rowwise").kp_norm_gate_rows, _ptr(o), _ptr(w), _ptr(g), _rows_2d(g, "g"), _ptr(out),
+         _rows_2d(out, "out"), n, d, ctypes.c_float(eps), dtype_code(g.dtype), STREAM)
+    return out
+
+
+def token_gate(gate: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor,
+               activation: str = "gelu_tanh") -> torch.Tensor:
+    """out[r, c] = act(gate[r, c]) * table[ids[r], col0 + c]."""
+    _need(gate, "gate", contiguous=False); _need(table, "table", gate.dtype, contiguous=False)
+    _need(ids, "ids", torch.int32); _need(out, "out", gate.dtype)
+    n, dim = gate.shape
+    if tuple(out.shape) != (n, dim) or ids.numel() != n or col0 < 0 or col0 + dim > table.shape[1]:
+        raise KernelError("token_gate: shape mismatch")
+    _run("token_gate", load_library("rowwise").kp_token_gate, _ptr(gate), _rows_2d(gate, "gate"), _ptr(table),
+         _rows_2d(table, "table"), int(col0), _ptr(ids), _ptr(out), n, dim, activation_code(activation),
+         dtype_code(gate.dtype), STREAM)
+    return out
+
+
+def rmsnorm_add_rows(y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor) -> torch.Tensor:
+    """x += rmsnorm(y) * w (all float32)."""
+    _need(y, "y", torch.float32); _need(w, "w", torch.float32); _need(x, "x", torch.float32)
+    n, d = x.shape
+    if tuple(y.shape) != (n, d) or w.numel() != d:
+        raise KernelError("rmsnorm_add_rows: shape mismatch")
+    _run("rmsnorm_add_rows", load_library("rowwise").kp_rmsnorm_add_rows, _ptr(y), _ptr(w), _ptr(x), n, d, ctypes.c_float(eps), STREAM)
+    return x
+
+
+def row_gate_add(h: torch.Tensor, w_gate: torch.Tensor, y: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] += sigmoid(h[r] . w_gate) * y[r]: ``w_gate`` float32 [d], ``y`` and ``out`` float32 [n, d]."""
+    _need(h, "h", contiguous=False); _need(w_gate, "w_gate", torch.float32); _need(y, "y", torch.float32)
+    _need(out, "out", torch.float32)
+    n, d = h.shape
+    if w_gate.numel() != d or tuple(y.shape) != (n, d) or tuple(out.shape) != (n, d):
+        raise KernelError("row_gate_add: shape mismatch")
+    _run("row_gate_add", load_library("rowwise").kp_row_gate_add, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate), _ptr(y), _ptr(out),
+         n, d, dtype_code(h.dtype), STREAM)
+    return out
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
@@ -450,6 +524,38 @@ def shortconv_update_state(p: torch.Tensor, state: torch.Tensor, cu_rows: torch.
     lib = load_library("shortconv")
     _run("shortconv_update_state", lib.kp_shortconv_update_state, _ptr(p), _rows_2d(p, "p"), _ptr(state), _ptr(cu_rows), _ptr(seg_pos),
                                          _ptr(seg_slot), n_seg, d, K, dtype_code(p.dtype), STREAM)
+
+
+# ------------------------------------------------------------------ linear attention with decay
+
+LIGHTNING_MAX_DIM = 256    # key rows of a head's state that the scan keeps in registers
+
+
+def lightning_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_hi: torch.Tensor, decay_lo: torch.Tensor,
+                   state: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor,
+                   out: torch.Tensor, n_seg: int, H: int, dim: int, vdim: int, activation: Optional[str] = "silu",
+                   write_state: bool = True) -> torch.Tensor:
+    """``S <- a_h S + k v^T; o = S^T q`` row after row of every segment, from the state in the segment's slot (zero at
+    position 0) and back into it.  q, k (H heads of ``dim``) and v (H heads of ``vdim``) are columns of ``qkv`` in
+    the storage type with ``activation`` (silu or None) applied here; ``out`` float32 [n, H vdim];
+    ``state`` float32 [slots, H, dim, vdim]; the decays as float32 pairs hi + lo [H]."""
+    _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)
+    _need(decay_hi, "decay_hi", torch.float32); _need(decay_lo, "decay_lo", torch.float32)
+    for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
+        _need(t, nm, torch.int32)
+    n = qkv.shape[0]
+    if (tuple(out.shape) != (n, H * vdim) or tuple(state.shape[1:]) != (H, dim, vdim) or decay_hi.numel() != H
+            or decay_lo.numel() != H or max(q_col, k_col) + H * dim > qkv.shape[1] or v_col + H * vdim > qkv.shape[1]):
+        raise KernelError("lightning_scan: shape mismatch")
+    if activation not in ("silu", None):
+        raise KernelError("lightning_scan: activation is silu or none")
+    if dim > LIGHTNING_MAX_DIM:
+        raise KernelError(f"lightning_scan: dim={dim} exceeds {LIGHTNING_MAX_DIM}")
+    _run("lightning_scan", load_library("lightning").kp_lightning_scan, _ptr(qkv), _rows_2d(qkv, "qkv"), int(q_col), int(k_col),
+         int(v_col), _ptr(decay_hi), _ptr(decay_lo), _ptr(state), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(out),
+         _rows_2d(out, "out"), int(n_seg), H, dim, vdim, 0 if activation == "silu" else 1, int(bool(write_state)),
+         dtype_code(qkv.dtype), STREAM, work=(4 * n * H * dim * vdim, 0))
+    return out
 
 
 # ------------------------------------------------------------------ attention
@@ -749,12 +855,12 @@ def gemm_stream_conv_step(a: torch.Tensor, w_in: torch.Tensor, bias: Optional[to
     return out
 
 
-FUSED_ACTIVATIONS = ("silu", "relu")     # what the products' gated epilogues compute themselves
+FUSED_ACTIVATIONS = ("silu", "relu", "gelu_tanh")     # what the products' gated epilogues compute themselves
 
 
 def _fused_activation(name: str) -> int:
     if name not in FUSED_ACTIVATIONS:
-        raise KernelError(f"the gated epilogue computes {' or '.join(FUSED_ACTIVATIONS)}, not '{name}'")
+        raise KernelError(f"the gated epilogue computes {', '.join(FUSED_ACTIVATIONS)}, not '{name}'")
     return activation_code(name)
 
 
@@ -825,19 +931,39 @@ def moe_layout_ints(n: int, E: int, top: int) -> int:
     return 3 * (E + 1) + 2 * n * top
 
 
-def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.Tensor, layout: torch.Tensor) -> None:
-    """Router logits [n, E] (float32) -> the ``top`` experts of every row (``idx`` int32 [n, top], largest logit
-    first, the lower index on ties), their weights (softmax over the chosen logits; float32 [n, top]) and the
+MOE_ROUTINGS = {"top_logits": 0, "softmax_all": 1}
+
+
+def _moe_routing(routing: str) -> int:
+    try:
+        return MOE_ROUTINGS[routing]
+    except KeyError:
+        raise KernelError(f"moe: routing '{routing}' (expected one of {', '.join(MOE_ROUTINGS)})") from None
+
+
+def moe_route(logits: torch.Tensor, top: int, idx: torch.Tensor, weights: torch.Tensor, layout: torch.Tensor,
+              bias: Optional[torch.Tensor] = None, routing: str = "top_logits", scale: float = 1.0,
+              n_identity: int = 0) -> None:
+    """Router logits [n, E] (float32) -> the ``top`` experts of every row (``idx`` int32 [n, top], largest
+    first, the lower index on ties), their weights (float32 [n, top]) and the
     layout of the (row, choice) pairs by expert (``layout``, int32, :func:`moe_layout_ints` words), which the
-    grouped products read.  Nothing returns to the host."""
+    grouped products read.  Nothing returns to the host.  ``routing`` ``top_logits``: the largest logits (+ ``bias``),
+    weighted by the softmax over the chosen logits alone; ``softmax_all``: scores = softmax over all E outputs, the
+    largest score + ``bias`` are chosen and weighted by their score times ``scale``.  The last ``n_identity``
+    outputs stand for experts without weights (places in the layout, no tiles)."""
     _need(logits, "logits", torch.float32); _need(idx, "idx", torch.int32); _need(weights, "weights", torch.float32)
     _need(layout, "layout", torch.int32)
     n, E = logits.shape
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != E:
+            raise KernelError("moe_route: bias size")
     if not (1 <= top <= min(E, MOE_MAX_TOP)) or E > MOE_MAX_EXPERTS:
         raise KernelError(f"moe_route: top={top} of {E} experts is not supported (top <= {MOE_MAX_TOP}, experts <= {MOE_MAX_EXPERTS})")
     if idx.numel() != n * top or weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
         raise KernelError("moe_route: output sizes")
-    _run("moe_route", load_library("moe").kp_moe_route, _ptr(logits), n, E, top, _ptr(idx), _ptr(weights), _ptr(layout), STREAM)
+    _run("moe_route", load_library("moe").kp_moe_route, _ptr(logits), _ptr(bias), n, E, top, _moe_routing(routing),
+         ctypes.c_float(scale), int(n_identity), _ptr(idx), _ptr(weights), _ptr(layout), STREAM)
     LAUNCHES[0] += 1
 
 
@@ -855,13 +981,14 @@ def moe_tc_status() -> int:
 
 
 def moe_router_ok(d: int, E: int) -> bool:
-    """Can the fused router kernel take rows of ``d`` elements and ``E`` experts (a row and its logits in shared memory)?"""
-    return d % 4 == 0 and E <= MOE_MAX_EXPERTS and (d + E) * 4 <= 200 * 1024
+    """Can the fused router kernel take rows of ``d`` elements and ``E`` experts (a row, its logits and its scores in shared memory)?"""
+    return d % 4 == 0 and E <= MOE_MAX_EXPERTS and (d + 2 * E) * 4 <= 200 * 1024
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
-               weights: torch.Tensor, layout: torch.Tensor) -> None:
-    """The router in one go: logits ``h w_router^T + bias`` in float32 (``w_router`` [E, d] and ``bias`` are float32;
+               weights: torch.Tensor, layout: torch.Tensor, routing: str = "top_logits", scale: float = 1.0,
+               n_identity: int = 0) -> None:
+    """The router in one go: logits ``h w_router^T`` in float32 (``w_router`` [E, d] and ``bias`` are float32;
     ``h`` is widened from its storage type), the choice and the layout as :func:`moe_route` leaves them."""
     _need(h, "h", contiguous=False); _need(w_router, "w_router", torch.float32)
     _need(idx, "idx", torch.int32); _need(weights, "weights", torch.float32); _need(layout, "layout", torch.int32)
@@ -876,32 +1003,40 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Ten
     if idx.numel() != n * top or weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
         raise KernelError("moe_router: output sizes")
     _run("moe_router", load_library("moe").kp_moe_router, _ptr(h), _rows_2d(h, "h"), _ptr(w_router), _ptr(bias), n, E, d, top,
-         _ptr(idx), _ptr(weights), _ptr(layout), dtype_code(h.dtype), STREAM,
+         _moe_routing(routing), ctypes.c_float(scale), int(n_identity), _ptr(idx), _ptr(weights), _ptr(layout), dtype_code(h.dtype), STREAM,
          work=(2 * n * E * d, n * d * h.element_size() + E * d * 4))
     LAUNCHES[0] += 1
 
 
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, layout: torch.Tensor,
-                weights: torch.Tensor, top: int, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+                weights: torch.Tensor, top: int, out: torch.Tensor, activation: str = "silu", n_identity: int = 0,
+                idx: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r] += sum_j weights[r, j] * Wd_e (act(Wg_e h[r]) * (Wu_e h[r])), e = the j-th expert of row r as laid out
     by :func:`moe_route`.  ``w_gate_up``: [E, 2 ff, d] (gate rows, then up rows); ``w_down``: [E, d, ff]; ``out``
-    float32 [n, d].  bfloat16 operands run on the tensor cores, float32 ones on the CUDA cores in true 32-bit."""
+    float32 [n, d].  bfloat16 operands run on the tensor cores, float32 ones on the CUDA cores in true 32-bit.
+    With ``n_identity`` the router had that many outputs more than there are experts here; a pair that chose one of
+    them (``idx`` [n, top] says so) adds ``weight * h[r]``."""
     _need(h, "h", contiguous=False); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
     _need(layout, "layout", torch.int32); _need(weights, "weights", torch.float32); _need(out, "out", torch.float32)
     n, d = h.shape
-    E, ff2, d2 = w_gate_up.shape
+    E_real, ff2, d2 = w_gate_up.shape
+    E = E_real + int(n_identity)
     ff = ff2 // 2
-    if d2 != d or ff2 != 2 * ff or tuple(w_down.shape) != (E, d, ff) or tuple(out.shape) != (n, d):
+    if d2 != d or ff2 != 2 * ff or tuple(w_down.shape) != (E_real, d, ff) or tuple(out.shape) != (n, d):
         raise KernelError("moe_experts: shape mismatch")
     if weights.numel() != n * top or layout.numel() < moe_layout_ints(n, E, top):
         raise KernelError("moe_experts: routing tables do not fit")
+    if n_identity:
+        _need(idx, "idx", torch.int32)
+        if idx.numel() != n * top:
+            raise KernelError("moe_experts: idx size")
     act = torch.empty((n * top, ff), dtype=h.dtype, device=h.device)
     y = torch.empty((n * top, d), dtype=torch.float32, device=h.device)
     # (many rows, 16-bit: the tcgen05 tiles read the rows laid out place by place)
     hs = torch.empty((n * top, d), dtype=h.dtype, device=h.device) if (h.dtype == torch.bfloat16 and n * top >= MOE_TC_MIN_PAIRS[0]) else None
     _run("moe_experts", load_library("moe").kp_moe_experts, _ptr(h), _rows_2d(h, "h"), _ptr(w_gate_up), _ptr(w_down), _ptr(layout),
          _ptr(weights), _ptr(act), _ptr(y), _ptr(out), _ptr(hs), n, E, top, d, ff, activation_code(activation), dtype_code(h.dtype),
-         STREAM, tag=f" {E}x{ff}x{d}",
+         int(n_identity), _ptr(idx if n_identity else None), STREAM, tag=f" {E}x{ff}x{d}",
          work=(6 * n * top * ff * d, min(E, n * top) * 3 * ff * d * h.element_size()))     # (bytes: the experts a step can touch)
     LAUNCHES[0] += 2
     return out

@@ -87,7 +87,78 @@ def attention_tiles(segs, split_ok: bool = True):
                  "n_short_tiles": n_short_seg})
 
 
-class Attention(Part):
+class PagedAttentionKernels:
+    """The choice among the attention kernels over the paged cache, shared by the mixers that keep keys and values
+    there.  The mixer has ``H``, ``G``, ``hd``, ``scale``, ``window``, ``block``, ``exact_weights``, ``split_ok``
+    and ``step_tables_key``."""
+
+    def _tile_setup(self):
+        # (the split-key kernel reads keys 16 bytes at a time and shares a kv head among at most 8 query heads;
+        # other shapes take the general kernel for every row)
+        self.split_ok = self.H // self.G <= K.SPLIT_MAX_RATIO and self.hd % 16 == 0
+        self.step_tables_key = ("attention_tiles", self.split_ok)
+
+    def step_tables(self, segs):
+        return attention_tiles(segs, self.split_ok)
+
+    def _attend(self, q, ctx, view, cache):
+        """Causal attention of the rows ``q`` [n, H hd] over the cache (this step's keys and values already in
+        it); returns the heads side by side."""
+        H, G, hd = self.H, self.G, self.hd
+        o = torch.empty_like(q)
+        tiles = ctx.tables.get(self.step_tables_key)
+        if self.split_ok and (tiles is None or q.dtype == torch.float32):
+            # rows that each read a long cache (decode): split the keys over many CTAs.  The 32-bit path
+            # takes this kernel for every row, whatever the length of its segment: its chunks lie at absolute
+            # multiples of 256 keys and are summed in order, so a row's bits do not depend on how the step was cut.
+            self._split(q, o, ctx, view, cache, ctx.n_rows)
+        elif tiles is not None and K.attention_prefill_ok(q, hd):
+            lead = tiles.n_short_rows
+            if lead and self.split_ok:
+                # decoded tokens beside prompt portions: the decoded rows lead the batch and go to the split
+                # kernel (in a row tile each would walk its whole cache alone), the portions to the tiled one
+                self._split(q, o, ctx, view, cache, lead)
+                t0 = tiles.n_short_tiles
+                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg[t0:],
+                                    tiles.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
+                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block, exact_weights=self.exact_weights)
+            else:
+                # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
+                big = (None, None) if lead else (tiles.big_tile_seg, tiles.big_tile_row0)
+                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
+                                    tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big,
+                                    block=self.block, exact_weights=self.exact_weights)
+        else:
+            lead = tiles.n_short_rows if tiles is not None else 0
+            if lead and self.split_ok:
+                self._split(q, o, ctx, view, cache, lead)
+            else:
+                lead = 0
+            K.attention_rows(q[lead:], cache.tensor, view.block_table, ctx.row_seg[lead:], ctx.positions[lead:], o[lead:],
+                             self.scale, self.window, view.page_size, H, G, hd, self.block)
+        return o
+
+    def _split(self, q, o, ctx, view, cache, n_rows):
+        """Split-key attention for the first ``n_rows`` rows of the step."""
+        H, G, hd = self.H, self.G, self.hd
+        n_chunks = -(-ctx.max_context // K.SPLIT_CHUNK)
+        need = K.attention_split_scratch(n_rows, H, hd, n_chunks)
+        ws = self.env.shared.get("attn_scratch")
+        if ws is None or ws.numel() < need:
+            # A captured decode step keeps the address of the scratch it was captured with, so a buffer that
+            # has been outgrown is retired, never freed: a replay of an older graph then still writes memory
+            # that nobody else owns.  Growth doubles, so the retired buffers together are smaller than the live one.
+            if ws is not None:
+                self.env.shared.setdefault("attn_scratch_retired", []).append(ws)
+            ws = torch.zeros(max(need, 2 * (ws.numel() if ws is not None else 0), 1 << 16), dtype=torch.float32,
+                             device=q.device)
+            self.env.shared["attn_scratch"] = ws
+        K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
+                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block,
+                          self.exact_weights)
+
+
+class Attention(PagedAttentionKernels, Part):
     category = "mixer"
     graph_safe = True
 
@@ -133,13 +204,7 @@ class Attention(Part):
         self.graph_safe = bool(self.position.graph_safe)     # a position part that reads host values keeps it eager
         if self.values_are_keys and not hasattr(self.position, "fused_rotary"):
             raise ConfigError("attention: values='keys' needs a position encoding that runs in the fused q/k kernel")
-        # (the split-key kernel reads keys 16 bytes at a time and shares a kv head among at most 8 query heads;
-        # other shapes take the general kernel for every row)
-        self.split_ok = self.H // self.G <= K.SPLIT_MAX_RATIO and self.hd % 16 == 0
-        self.step_tables_key = ("attention_tiles", self.split_ok)
-
-    def step_tables(self, segs):
-        return attention_tiles(segs, self.split_ok)
+        self._tile_setup()
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         d, H, G, hd = self.d, self.H, self.G, self.hd
@@ -199,60 +264,111 @@ class Attention(Part):
             self.position.apply(qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], ctx)
             K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q, kv_out,
                               view.page_size, H, G, hd)
-        o = torch.empty_like(q)
-        tiles = ctx.tables.get(self.step_tables_key)
-        if self.split_ok and (tiles is None or q.dtype == torch.float32):
-            # rows that each read a long cache (decode): split the keys over many CTAs.  The 32-bit path
-            # takes this kernel for every row, whatever the length of its segment: its chunks lie at absolute
-            # multiples of 256 keys and are summed in order, so a row's bits do not depend on how the step was cut.
-            self._split(q, o, ctx, view, cache, ctx.n_rows)
-        elif tiles is not None and K.attention_prefill_ok(q, hd):
-            lead = tiles.n_short_rows
-            if lead and self.split_ok:
-                # decoded tokens beside prompt portions: the decoded rows lead the batch and go to the split
-                # kernel (in a row tile each would walk its whole cache alone), the portions to the tiled one
-                self._split(q, o, ctx, view, cache, lead)
-                t0 = tiles.n_short_tiles
-                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg[t0:],
-                                    tiles.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
-                                    tiles.big_tile_seg, tiles.big_tile_row0, block=self.block, exact_weights=self.exact_weights)
-            else:
-                # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
-                big = (None, None) if lead else (tiles.big_tile_seg, tiles.big_tile_row0)
-                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, tiles.tile_seg,
-                                    tiles.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big,
-                                    block=self.block, exact_weights=self.exact_weights)
-        else:
-            lead = tiles.n_short_rows if tiles is not None else 0
-            if lead and self.split_ok:
-                self._split(q, o, ctx, view, cache, lead)
-            else:
-                lead = 0
-            K.attention_rows(q[lead:], cache.tensor, view.block_table, ctx.row_seg[lead:], ctx.positions[lead:], o[lead:],
-                             self.scale, self.window, view.page_size, H, G, hd, self.block)
+        o = self._attend(q, ctx, view, cache)
         if self.gated:
             K.sigmoid_gate(o, qkv[:, self.gate_col:self.gate_col + H * hd])
         linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
 
 
-    def _split(self, q, o, ctx, view, cache, n_rows):
-        """Split-key attention for the first ``n_rows`` rows of the step."""
-        H, G, hd = self.H, self.G, self.hd
-        n_chunks = -(-ctx.max_context // K.SPLIT_CHUNK)
-        need = K.attention_split_scratch(n_rows, H, hd, n_chunks)
-        ws = self.env.shared.get("attn_scratch")
-        if ws is None or ws.numel() < need:
-            # A captured decode step keeps the address of the scratch it was captured with, so a buffer that
-            # has been outgrown is retired, never freed: a replay of an older graph then still writes memory
-            # that nobody else owns.  Growth doubles, so the retired buffers together are smaller than the live one.
-            if ws is not None:
-                self.env.shared.setdefault("attn_scratch_retired", []).append(ws)
-            ws = torch.zeros(max(need, 2 * (ws.numel() if ws is not None else 0), 1 << 16), dtype=torch.float32,
-                             device=q.device)
-            self.env.shared["attn_scratch"] = ws
-        K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
-                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd, self.block,
-                          self.exact_weights)
+class LatentAttention(PagedAttentionKernels, Part):
+    """Attention whose queries, keys and values are expanded from low-rank latents, without positions.
+
+    ``c_q = norm(h Wdq^T) * w_q``, ``q = c_q Wuq^T``; ``c = norm(h Wdkv^T) * w_kv``, ``k = c Wuk^T``,
+    ``v = c Wuv^T`` (every head has keys and values of its own, ``head_dim`` and ``value_dim`` wide); causal
+    softmax attention with ``scale``; the concatenated heads times ``sigmoid(h Wg^T)`` (``gate`` = ``"sigmoid"``),
+    then the output matrix.  The two down-projections and the gate read the same input and run as one product;
+    the two latents are normed by one launch; the expanded keys and values go to the paged cache, one kv head a
+    query head, and the attention kernels of :class:`Attention` run over it unchanged.  A cache head is as wide
+    as the wider of ``head_dim`` and ``value_dim``, rounded up to a multiple of 16 (the expanding matrices, the
+    gate's and the output matrix get zero rows or columns for that at load, so that nothing pads at run time).
+
+    Params: hidden_size, num_heads, head_dim, value_dim, q_rank, kv_rank, scale, norm_eps, gate (None |
+    "sigmoid"), softmax_weights ("operand" | "float32"), window, block.
+    """
+
+    category = "mixer"
+    graph_safe = True
+
+    def __init__(self, params, env):
+        super().__init__(params, env)
+        self.d = int(self._p("hidden_size"))
+        self.H = int(self._p("num_heads"))
+        self.dim = int(self._p("head_dim"))
+        self.vdim = int(self._p("value_dim", self.dim))
+        self.q_rank = int(self._p("q_rank"))
+        self.kv_rank = int(self._p("kv_rank"))
+        self.scale = float(self._p("scale"))
+        self.eps = float(self._p("norm_eps"))
+        self.window: Optional[int] = self._p("window", None)
+        self.block: Optional[int] = self._p("block", None)
+        gate = self._p("gate", None)
+        if gate not in (None, "sigmoid"):
+            raise ConfigError(f"latent_attention: gate='{gate}' (expected 'sigmoid' or none)")
+        self.gated = gate is not None
+        sw = self._p("softmax_weights", "operand")
+        if sw not in ("operand", "float32"):
+            raise ConfigError(f"latent_attention: softmax_weights='{sw}' (expected 'operand' or 'float32')")
+        self.exact_weights = sw == "float32"
+        if min(self.H, self.dim, self.vdim, self.q_rank, self.kv_rank) < 1:
+            raise ConfigError("latent_attention: heads, head sizes and ranks must be positive")
+        self.G = self.H                                          # the expanded keys and values are per head
+        self.hd = -(-max(self.dim, self.vdim) // 16) * 16        # width of a head in the cache
+        if self.hd > 256:
+            raise ConfigError(f"latent_attention: heads of {max(self.dim, self.vdim)} are not supported by the kernels (at most 256)")
+        self._tile_setup()
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        d, H = self.d, self.H
+        s = {"q_down.weight": WeightSpec((self.q_rank, d)), "q_norm.weight": WeightSpec((self.q_rank,), "norm"),
+             "q_up.weight": WeightSpec((H * self.dim, self.q_rank)),
+             "kv_down.weight": WeightSpec((self.kv_rank, d)), "kv_norm.weight": WeightSpec((self.kv_rank,), "norm"),
+             "k_up.weight": WeightSpec((H * self.dim, self.kv_rank)), "v_up.weight": WeightSpec((H * self.vdim, self.kv_rank)),
+             "out_proj.weight": WeightSpec((d, H * self.vdim))}
+        if self.gated:
+            s["gate_proj.weight"] = WeightSpec((H * self.vdim, d))
+        return s
+
+    def _pad_rows(self, w, width):
+        """[H width, k] -> [H hd, k]: every head's rows, then zero rows up to the cache head's width."""
+        if width == self.hd:
+            return w.contiguous()
+        out = torch.zeros((self.H, self.hd, w.shape[1]), dtype=w.dtype, device=w.device)
+        out[:, :width] = w.reshape(self.H, width, w.shape[1])
+        return out.reshape(self.H * self.hd, w.shape[1])
+
+    def bind(self, w):
+        rows = [w["q_down.weight"], w["kv_down.weight"]]
+        if self.gated:
+            rows.append(self._pad_rows(w["gate_proj.weight"], self.vdim))
+        self.w_down = torch.cat(rows, 0).contiguous()
+        self.gate_col = self.q_rank + self.kv_rank
+        self.q_norm_w = w["q_norm.weight"].float().contiguous()
+        self.kv_norm_w = w["kv_norm.weight"].float().contiguous()
+        self.w_uq = self._pad_rows(w["q_up.weight"], self.dim)
+        self.w_ukv = torch.cat([self._pad_rows(w["k_up.weight"], self.dim), self._pad_rows(w["v_up.weight"], self.vdim)], 0).contiguous()
+        self.w_o = self._pad_rows(w["out_proj.weight"].t().contiguous(), self.vdim).t().contiguous()
+
+    def cache_spec(self):
+        return PagedKVSpec(self.H, self.hd, self.window, None if self.block is None else int(self.block))
+
+    def forward(self, h, residual, ctx, cache):
+        H, hd, n = self.H, self.hd, ctx.n_rows
+        view = ctx.paged[cache.group]
+        p = linear(h, self.w_down)                               # [c_q before its norm | c before its norm | gate]
+        cq = torch.empty((n, self.q_rank), dtype=p.dtype, device=p.device)
+        c = torch.empty((n, self.kv_rank), dtype=p.dtype, device=p.device)
+        K.rmsnorm_cols(p, [(0, self.q_norm_w, cq), (self.q_rank, self.kv_norm_w, c)], self.eps)
+        qkv = torch.empty((n, 3 * H * hd), dtype=p.dtype, device=p.device)
+        linear(cq, self.w_uq, out=qkv[:, :H * hd])
+        linear(c, self.w_ukv, out=qkv[:, H * hd:])
+        q = torch.empty((n, H * hd), dtype=p.dtype, device=p.device)
+        K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q,
+                          cache.tensor if cache.writes else None, view.page_size, H, H, hd)
+        o = self._attend(q, ctx, view, cache)
+        if self.gated:
+            K.sigmoid_gate(o, p[:, self.gate_col:self.gate_col + H * hd])
+        linear(o, self.w_o, out=residual, accumulate=True)
 
 
 register_part("mixer", "attention", Attention)
+register_part("mixer", "latent_attention", LatentAttention)

@@ -25,6 +25,11 @@ any             optionally ``step_tables_key`` and ``step_tables(segs)``: int32
 ``block``         ``forward(x, ctx, cache)``: the arrangement of the above
                   around the float32 residual ``x``.
 ``embedding`` / ``head``  token ids -> residual rows; selected rows -> logits.
+``side``          ``forward(x, ctx)``: changes the residual in place at the end
+                  of a layer (a per-layer token input).
+``entry``         ``forward(x, h0)`` -> the new residual at the head of a
+                  schedule entry marked ``enter`` (``h0``: the embedding output
+                  in the compute type).
 """
 from __future__ import annotations
 
@@ -96,7 +101,7 @@ class Part:
 
 
 _REGISTRY: Dict[Tuple[str, str], Callable[..., Part]] = {}
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "side", "entry")
 
 
 def register_part(category: str, kind: str, factory: Callable[..., Part], *, replace: bool = False) -> None:
@@ -133,4 +138,4 @@ def _ensure_builtin() -> None:
     global _builtin
     if not _builtin:
         _builtin = True
-        from . import norm, position, attention, shortconv, ffn, block, embedding  # noqa: F401
+        from . import norm, position, attention, shortconv, lightning, ffn, block, embedding, side  # noqa: F401

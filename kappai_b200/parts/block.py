@@ -2,7 +2,8 @@
 
 ``prenorm_residual``: ``x += mixer(norm1(x)); x += ffn(norm2(x))``
 (src/models/lfm.c:7-53 followed by src/recipe/builders.c:378-388).  The
-residual ``x`` is float32 and is updated in place.
+residual ``x`` is float32 and is updated in place.  A ``side`` part, if the
+layer has one, then changes the residual once more (``side.forward(x, ctx)``).
 
 ``postnorm_residual``: ``x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ffn(x))``:
 the sublayers read ``x`` itself (in the compute type), the norm comes after the
@@ -24,14 +25,16 @@ class PreNormResidualBlock(Part):
     category = "block"
     graph_safe = True
 
-    def assemble(self, mixer, ffn, mixer_norm, ffn_norm):
-        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+    def assemble(self, mixer, ffn, mixer_norm, ffn_norm, side=None):
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm, self.side = mixer, ffn, mixer_norm, ffn_norm, side
         return self
 
     def forward(self, x, ctx, cache):
         self.mixer.forward(self.mixer_norm.forward(x) if self.mixer_norm is not None else x, x, ctx, cache)
         if self.ffn is not None:
             self.ffn.forward(self.ffn_norm.forward(x) if self.ffn_norm is not None else x, x, ctx)
+        if self.side is not None:
+            self.side.forward(x, ctx)
 
 
 class PostNormResidualBlock(Part):
@@ -42,10 +45,12 @@ class PostNormResidualBlock(Part):
         super().__init__(params, env)
         self.alpha = float(self._p("alpha", 1.0))
 
-    def assemble(self, mixer, ffn, mixer_norm, ffn_norm):
+    def assemble(self, mixer, ffn, mixer_norm, ffn_norm, side=None):
         if mixer_norm is None or (ffn is not None and ffn_norm is None):
             raise ValueError("postnorm_residual: every sublayer needs the norm that follows its sum")
-        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+        if side is not None:
+            raise ValueError("postnorm_residual: no side part in this arrangement")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm, self.side = mixer, ffn, mixer_norm, ffn_norm, None
         return self
 
     def _enter(self, x, ctx):

@@ -13,6 +13,15 @@ kind ``glu``).
 row uses the ``top`` with the largest router logits ``z = h Wr^T + b`` (float32),
 weighted by the softmax over those ``top`` logits alone; see csrc/moe.cu.
 Params: hidden_size, expert_size, num_experts, top, activation, router_bias.
+More of them, each off by default: ``routing`` = ``"softmax_all"`` takes as
+scores the softmax over all router outputs, chooses by score + a learned
+``correction`` (a tensor; it takes part in the choice only) and weighs a chosen
+expert by its score times ``router_scale``, without renormalising;
+``identity_experts``: that many further router outputs stand for experts that
+return their input (they have no tensors); ``shared_size``: a unit of that size
+which every row uses beside its chosen experts, its output times
+``sigmoid(w_sg . h)``, one gate a row (``shared_gate`` = ``"sigmoid"``) or
+ungated (None).
 """
 from __future__ import annotations
 
@@ -71,17 +80,43 @@ class MixtureOfExperts(Part):
         self.E = int(self._p("num_experts"))
         self.top = int(self._p("top"))
         self.activation = str(self._p("activation", "silu"))
-        self.router_bias = bool(self._p("router_bias", True))
+        self.routing = str(self._p("routing", "top_logits"))
+        if self.routing not in K.MOE_ROUTINGS:
+            raise ConfigError(f"moe: routing='{self.routing}' (expected one of {', '.join(K.MOE_ROUTINGS)})")
+        self.router_bias = bool(self._p("router_bias", self.routing == "top_logits"))
+        self.correction = bool(self._p("correction", self.routing == "softmax_all"))
+        self.router_scale = float(self._p("router_scale", 1.0))
+        self.n_identity = int(self._p("identity_experts", 0))
+        self.E_all = self.E + self.n_identity                       # router outputs
+        shared = self._p("shared_size", None)
+        self.shared_ff = None if shared is None else int(shared)
+        self.shared_gate = self._p("shared_gate", None)
         K.activation_code(self.activation)
-        if self.E < 1 or not (1 <= self.top <= self.E):
-            raise ConfigError(f"moe: top={self.top} must lie between 1 and num_experts={self.E}")
-        if self.top > K.MOE_MAX_TOP or self.E > K.MOE_MAX_EXPERTS:
-            raise ConfigError(f"moe: the kernels take top <= {K.MOE_MAX_TOP} and num_experts <= {K.MOE_MAX_EXPERTS}")
+        if self.E < 1 or self.n_identity < 0 or not (1 <= self.top <= self.E_all):
+            raise ConfigError(f"moe: top={self.top} must lie between 1 and the {self.E_all} router outputs")
+        if self.top > K.MOE_MAX_TOP or self.E_all > K.MOE_MAX_EXPERTS:
+            raise ConfigError(f"moe: the kernels take top <= {K.MOE_MAX_TOP} and at most {K.MOE_MAX_EXPERTS} router outputs")
+        if self.routing == "top_logits" and self.correction:
+            raise ConfigError("moe: a correction of the choice belongs to routing='softmax_all'")
+        if self.routing == "softmax_all" and self.router_bias:
+            raise ConfigError("moe: routing='softmax_all' has a correction of the choice, not a bias of the logits")
+        if self.shared_gate not in (None, "sigmoid"):
+            raise ConfigError(f"moe: shared_gate='{self.shared_gate}' (expected 'sigmoid' or none)")
+        if self.shared_ff is not None and self.shared_ff < 1:
+            raise ConfigError("moe: shared_size must be positive")
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        s = {"router.weight": WeightSpec((self.E, self.d))}
+        s = {"router.weight": WeightSpec((self.E_all, self.d))}
         if self.router_bias:
-            s["router.bias"] = WeightSpec((self.E,), "bias")
+            s["router.bias"] = WeightSpec((self.E_all,), "bias")
+        if self.correction:
+            s["router.correction"] = WeightSpec((self.E_all,), "bias")
+        if self.shared_ff is not None:
+            s["shared.gate_proj.weight"] = WeightSpec((self.shared_ff, self.d))
+            s["shared.up_proj.weight"] = WeightSpec((self.shared_ff, self.d))
+            s["shared.down_proj.weight"] = WeightSpec((self.d, self.shared_ff))
+            if self.shared_gate is not None:
+                s["shared.gate.weight"] = WeightSpec((1, self.d))
         for e in range(self.E):
             s[f"experts.{e}.gate_proj.weight"] = WeightSpec((self.ff, self.d))
             s[f"experts.{e}.up_proj.weight"] = WeightSpec((self.ff, self.d))
@@ -92,6 +127,14 @@ class MixtureOfExperts(Part):
         # the router is 32-bit whatever the storage of the rest
         self.w_router = w["router.weight"].to(torch.float32).contiguous()
         self.b_router = w["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
+        if self.correction:
+            self.b_router = w["router.correction"].to(torch.float32).contiguous()
+        self.ws_gu = self.ws_down = self.ws_gate = None
+        if self.shared_ff is not None:
+            self.ws_gu = torch.cat([w["shared.gate_proj.weight"], w["shared.up_proj.weight"]], 0).contiguous()
+            self.ws_down = w["shared.down_proj.weight"].contiguous()
+            if self.shared_gate is not None:
+                self.ws_gate = w["shared.gate.weight"].to(torch.float32).reshape(-1).contiguous()
         self.w_gu = torch.stack([torch.cat([w[f"experts.{e}.gate_proj.weight"], w[f"experts.{e}.up_proj.weight"]], 0)
                                  for e in range(self.E)]).contiguous()                       # [E, 2 ff, d]
         self.w_down = torch.stack([w[f"experts.{e}.down_proj.weight"] for e in range(self.E)]).contiguous()   # [E, d, ff]
@@ -100,13 +143,25 @@ class MixtureOfExperts(Part):
         n = h.shape[0]
         idx = torch.empty((n, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((n, self.top), dtype=torch.float32, device=h.device)
-        layout = torch.empty(K.moe_layout_ints(n, self.E, self.top), dtype=torch.int32, device=h.device)
-        if K.moe_router_ok(self.d, self.E) and h.stride(1) == 1:
-            K.moe_router(h, self.w_router, self.b_router, self.top, idx, weights, layout)
-        else:
+        layout = torch.empty(K.moe_layout_ints(n, self.E_all, self.top), dtype=torch.int32, device=h.device)
+        how = dict(routing=self.routing, scale=self.router_scale, n_identity=self.n_identity)
+        if K.moe_router_ok(self.d, self.E_all) and h.stride(1) == 1:
+            K.moe_router(h, self.w_router, self.b_router, self.top, idx, weights, layout, **how)
+        elif self.routing == "top_logits":
             logits = linear(h, self.w_router, self.b_router, out_dtype=torch.float32)
-            K.moe_route(logits, self.top, idx, weights, layout)
-        K.moe_experts(h, self.w_gu, self.w_down, layout, weights, self.top, residual, self.activation)
+            K.moe_route(logits, self.top, idx, weights, layout, **how)
+        else:
+            logits = linear(h, self.w_router, None, out_dtype=torch.float32)
+            K.moe_route(logits, self.top, idx, weights, layout, bias=self.b_router, **how)
+        K.moe_experts(h, self.w_gu, self.w_down, layout, weights, self.top, residual, self.activation,
+                      n_identity=self.n_identity, idx=idx)
+        if self.ws_gu is not None:
+            act = linear_swiglu(h, self.ws_gu, None, self.activation)
+            if self.ws_gate is None:
+                linear(act, self.ws_down, None, out=residual, accumulate=True)
+            else:
+                y = linear(act, self.ws_down, None, out_dtype=torch.float32)
+                K.row_gate_add(h, self.ws_gate, y, residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

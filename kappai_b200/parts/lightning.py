@@ -1,0 +1,93 @@
+"""Linear attention with a per-head decay ("lightning attention").
+
+``q, k, v = act(h Wq^T), act(h Wk^T), act(h Wv^T)`` (act = silu; heads side by
+side, ``head_dim`` wide for q and k, ``value_dim`` for v); for every head a
+state ``S`` [head_dim, value_dim] follows the recurrence
+
+    S_t = a_h S_(t-1) + k_t v_t^T ,   o_t = S_t^T q_t
+
+with one constant decay ``a_h`` a head and no other scale.  The heads of ``o``
+side by side are RMS-normed as one row with a weight, multiplied by
+``sigmoid(h Wg^T)`` and projected by the output matrix into the residual.  The
+state is the request's only memory of this mixer: float32, one slot a request,
+zero at position 0.  The four matrices that read the layer's input run as one
+product; the recurrence, the norm and the gate are float32 (csrc/lightning.cu,
+``norm_gate_rows``).
+
+Params: hidden_size, num_heads, head_dim, value_dim, decay (a list, one a
+head), norm_eps, activation ("silu" | None), gate ("sigmoid").
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+import torch
+
+from ..cache.spec import StateSpec
+from ..config.schema import ConfigError
+from ..ops import kernels as K
+from ..ops.linear import linear
+from .base import Part, WeightSpec, register_part
+
+
+class LightningAttention(Part):
+    category = "mixer"
+    graph_safe = True
+
+    def __init__(self, params, env):
+        super().__init__(params, env)
+        self.d = int(self._p("hidden_size"))
+        self.H = int(self._p("num_heads"))
+        self.dim = int(self._p("head_dim"))
+        self.vdim = int(self._p("value_dim", self.dim))
+        self.eps = float(self._p("norm_eps"))
+        self.activation = self._p("activation", "silu")
+        decay = self._p("decay")
+        if not isinstance(decay, (list, tuple)) or len(decay) != self.H:
+            raise ConfigError(f"lightning: decay must list one number for each of the {self.H} heads")
+        self.decay = [float(a) for a in decay]
+        if any(not (0.0 <= a <= 1.0) for a in self.decay):
+            raise ConfigError("lightning: a decay lies between 0 and 1")
+        if self.activation not in ("silu", None):
+            raise ConfigError(f"lightning: activation='{self.activation}' (expected 'silu' or none)")
+        if self._p("gate", "sigmoid") != "sigmoid":
+            raise ConfigError("lightning: the output gate is a sigmoid")
+        if min(self.H, self.dim, self.vdim) < 1 or self.dim > K.LIGHTNING_MAX_DIM:
+            raise ConfigError(f"lightning: head_dim={self.dim} is not supported by the kernels (1 to {K.LIGHTNING_MAX_DIM})")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        d, H = self.d, self.H
+        return {"q_proj.weight": WeightSpec((H * self.dim, d)), "k_proj.weight": WeightSpec((H * self.dim, d)),
+                "v_proj.weight": WeightSpec((H * self.vdim, d)), "gate_proj.weight": WeightSpec((H * self.vdim, d)),
+                "out_proj.weight": WeightSpec((d, H * self.vdim)), "norm.weight": WeightSpec((H * self.vdim,), "norm")}
+
+    def bind(self, w):
+        self.w_in = torch.cat([w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"], w["gate_proj.weight"]], 0).contiguous()
+        self.w_o = w["out_proj.weight"].contiguous()
+        self.norm_w = w["norm.weight"].float().contiguous()
+        # a decay as a float32 pair: hi the nearest float32, lo what it leaves of the constant
+        a = np.asarray(self.decay, dtype=np.float64)
+        hi = a.astype(np.float32)
+        lo = (a - hi.astype(np.float64)).astype(np.float32)
+        dev = self.w_in.device
+        self.decay_hi = torch.from_numpy(hi).to(dev)
+        self.decay_lo = torch.from_numpy(lo).to(dev)
+
+    def cache_spec(self):
+        return StateSpec((self.H, self.dim, self.vdim), "float32")
+
+    def forward(self, h, residual, ctx, cache):
+        """``cache``: a :class:`~kappai_b200.cache.storage.StateView` with tensor [n_slots, H, head_dim, value_dim]."""
+        H, dim, vdim, n = self.H, self.dim, self.vdim, ctx.n_rows
+        p = linear(h, self.w_in)                                 # [q | k | v | gate]
+        o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
+        K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows, ctx.seg_pos,
+                         ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
+        g0 = 2 * H * dim + H * vdim
+        og = torch.empty((n, H * vdim), dtype=p.dtype, device=p.device)
+        K.norm_gate_rows(o, self.norm_w, p[:, g0:g0 + H * vdim], self.eps, og)
+        linear(og, self.w_o, out=residual, accumulate=True)
+
+
+register_part("mixer", "lightning", LightningAttention)
