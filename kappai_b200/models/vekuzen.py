@@ -78,9 +78,9 @@ class VekuzenConfig(TypedConfig):
         if self.eps <= 0:
             raise ConfigError("norm.eps must be positive")
         self.embedding_scale = float(_get(self.embedding, "scale", "embedding"))
-        self.side_dim = _int(self.token_side, "dim", "token_side") if self.token_side else None
+        self.side_dim = _int(self.token_side, "dim", "token_side") if self.token_side is not None else None
         n = len(self.layers)
-        if self.loop:
+        if self.loop is not None:
             a, b = _int(self.loop, "start", "loop", 0), _int(self.loop, "stop", "loop", 0)
             _int(self.loop, "times", "loop")
             if not (0 <= a < b <= n):
@@ -169,7 +169,7 @@ def _ffn_spec(c: VekuzenConfig, mlp: Optional[Dict[str, Any]], prefix: str) -> O
 def layer_schedule(c: VekuzenConfig) -> List[ScheduleEntry]:
     """The order in which the layers run: the looped stretch ``times`` times, the head of every pass marked."""
     n = len(c.layers)
-    if not c.loop:
+    if c.loop is None:
         return [ScheduleEntry(i) for i in range(n)]
     a, b, times = int(c.loop["start"]), int(c.loop["stop"]), int(c.loop["times"])
     sched = [ScheduleEntry(i) for i in range(a)]
@@ -206,7 +206,7 @@ def build_spec(c: VekuzenConfig) -> ModelSpec:
         head=PartSpec("lm_head", {"vocab_size": c.vocab, "hidden_size": c.width, "tied": False,
                                   "scale": float(c.logit_scale)}, "", rename={"weight": "head"}),
         eos_token_id=c.eos_token_id,
-        entry=PartSpec("concat_linear", {"hidden_size": c.width}, "", rename={"weight": "loop.in"}) if c.loop else None,
+        entry=PartSpec("concat_linear", {"hidden_size": c.width}, "", rename={"weight": "loop.in"}) if c.loop is not None else None,
         token_table=(PartSpec("token_table", {"vocab_size": c.vocab, "width": c.side_dim * len(c.layers)}, "",
                               rename={"weight": "side.embed"}) if c.side_dim is not None else None),
     )

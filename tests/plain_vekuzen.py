@@ -91,12 +91,11 @@ def lightning(h, wq, wk, wv, wg, wo, norm_w, decay, heads, dim, vdim, eps, state
     k = silu(h @ wk.T).reshape(T, heads, dim)
     v = silu(h @ wv.T).reshape(T, heads, vdim)
     S = np.zeros((heads, dim, vdim)) if state is None else np.array(state, dtype=np.float64)
-    a = np.asarray(decay, dtype=np.float64)
+    a = np.asarray(decay, dtype=np.float64)[:, None, None]
     o = np.empty((T, heads, vdim))
-    for t in range(T):
-        for j in range(heads):
-            S[j] = a[j] * S[j] + np.outer(k[t, j], v[t, j])
-            o[t, j] = S[j].T @ q[t, j]
+    for t in range(T):                                             # (all heads at once: S [heads, dim, vdim])
+        S = a * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = np.einsum("hdv,hd->hv", S, q[t])
     o = rms_norm(o.reshape(T, heads * vdim), norm_w, eps) * sigmoid(h @ wg.T)
     return o @ wo.T, S
 
@@ -105,13 +104,14 @@ def causal_softmax_attention(q, k, v, scale, first_key=None):
     """q, k [T, H, dim], v [T, H, vdim]; row i reads keys j <= i (and j >= first_key[i] if given)."""
     T, H, _ = q.shape
     out = np.empty((T, H, v.shape[2]))
-    for i in range(T):
-        lo = 0 if first_key is None else int(first_key[i])
-        for j in range(H):
-            s = (k[lo:i + 1, j] @ q[i, j]) * scale
-            w = np.exp(s - s.max())
-            w /= w.sum()
-            out[i, j] = w @ v[lo:i + 1, j]
+    i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+    seen = j <= i
+    if first_key is not None:
+        seen &= j >= np.asarray(first_key)[:, None]
+    for h in range(H):                                             # (a head at a time: scores [T, T])
+        s = np.where(seen, (q[:, h] @ k[:, h].T) * scale, -np.inf)
+        w = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, h] = (w / w.sum(axis=1, keepdims=True)) @ v[:, h]
     return out
 
 
@@ -140,6 +140,14 @@ def route(h, w_router, correction, top, scale):
     choice = s + correction
     idx = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
     return idx, np.take_along_axis(s, idx, axis=-1) * scale, s
+
+
+def choice_margin(h, w_router, correction, top):
+    """For every row the gap between the last chosen and the first unchosen choice score (inf if all are chosen)."""
+    z = h @ w_router.T
+    s = np.exp(z - z.max(axis=-1, keepdims=True))
+    c = np.sort(s / s.sum(axis=-1, keepdims=True) + correction, axis=-1)[:, ::-1]
+    return c[:, top - 1] - c[:, top] if top < c.shape[1] else np.full(h.shape[0], np.inf)
 
 
 def mixture(h, w_router, correction, experts, n_identity, top, scale, shared=None):
@@ -203,7 +211,7 @@ class PlainVekuzen:
                                     float(m["scale"]), self.eps)
         raise ValueError(L["type"])
 
-    def _ff(self, i, h):
+    def _ff(self, i, h, margins=None):
         mlp, w, p = self.cfg["layers"][i]["mlp"], self.w, f"l{i}.mlp."
         if mlp["kind"] == "dense":
             return gated_unit(h, w[p + "gate"], w[p + "up"], w[p + "down"], gelu_tanh)
@@ -213,10 +221,13 @@ class PlainVekuzen:
         shared = None
         if mlp.get("shared"):
             shared = (w[p + "shared.gate"], w[p + "shared.up"], w[p + "shared.down"], w[p + "shared.sg"])
+        if margins is not None:
+            margins.append(choice_margin(h, w[p + "router"], w[p + "correction"], int(r["top"])))
         return mixture(h, w[p + "router"], w[p + "correction"], experts, ident, int(r["top"]), float(r["scale"]), shared)
 
-    def forward(self, tokens, layers_out=None):
-        """Logits [T, vocab] of a whole sequence; ``layers_out`` (a list) gets the residual after every layer run."""
+    def forward(self, tokens, layers_out=None, margins=None):
+        """Logits [T, vocab] of a whole sequence; ``layers_out`` (a list) gets the residual after every layer run,
+        ``margins`` (a list) every mixture's choice margins [T]."""
         cfg, w = self.cfg, self.w
         x = embed(tokens, w["embed"], float(cfg["embedding"]["scale"]), w["pos"])
         x0 = x.copy()
@@ -227,7 +238,7 @@ class PlainVekuzen:
             p = f"l{i}."
             x = x + self._mixer(i, rms_norm(x, w[p + "norm1"], self.eps))
             if cfg["layers"][i].get("mlp") is not None:
-                x = x + self._ff(i, rms_norm(x, w[p + "norm2"], self.eps))
+                x = x + self._ff(i, rms_norm(x, w[p + "norm2"], self.eps), margins)
             if side:
                 x = token_side(x, tokens, w["side.embed"], i, int(side["dim"]), w[p + "side.gate"], w[p + "side.proj"],
                                w[p + "side.norm"], self.eps)

@@ -1,0 +1,527 @@
+"""Vekuzen on the GPU: every new mechanism's kernel against the plain functions, the two mixers as parts in batches
+cut in two, then whole models through the step function, the trace runner and the engine in every way of cutting
+the work."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vekuzen as P
+import replay_util as R
+from tolerances import tol_for
+from vekuzen_configs import CONFIGS, make_model_dir
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a), dtype=torch.float32).to(DEV).to(dtype).contiguous()
+
+
+def i32(a):
+    return torch.as_tensor(np.asarray(a), dtype=torch.int32).to(DEV)
+
+
+def rt(a, dtype):
+    """The values that survive storage in ``dtype``."""
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(dtype).double().numpy()
+
+
+@pytest.fixture(scope="module")
+def vek_dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("vekuzen")
+    return {n: make_model_dir(n, str(root)) for n in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def vek_plain(vek_dirs):
+    return {n: P.PlainVekuzen(d) for n, d in vek_dirs.items()}
+
+
+# ------------------------------------------------------------------------------------- mechanisms alone
+
+def _plain_recurrence(q, k, v, decay, state=None):
+    """o_t and the final state of S_t = a S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; q, k [T, H, dim], v [T, H, vdim]."""
+    T, H, dim = q.shape
+    S = np.zeros((H, dim, v.shape[2])) if state is None else state.copy()
+    o = np.empty((T, H, v.shape[2]))
+    for t in range(T):
+        for j in range(H):
+            S[j] = decay[j] * S[j] + np.outer(k[t, j], v[t, j])
+            o[t, j] = S[j].T @ q[t, j]
+    return o, S
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dim,vdim,decay", [
+    (2, 16, 32, [0.9, 0.995]), (3, 40, 24, [0.3, 1.0, 0.999]), (1, 128, 64, [0.97]), (2, 256, 8, [0.5, 0.99]),
+    (1, 1, 1, [0.75]), (4, 64, 64, [0.6, 0.9, 0.99, 0.9999])])
+def test_lightning_scan_segments_states_and_slots(H, dim, vdim, decay, dtype):
+    """Three requests in one launch (a whole prompt, a continuation from a state that an earlier launch left, one
+    token), then one-token steps; slots in another order than the segments; a slot that held another request's
+    state is zeroed by position 0 alone."""
+    from kappai_b200.ops import kernels as K
+    rng = np.random.default_rng(dim * 7 + vdim)
+    lens, cut = [37, 50, 1], [37, 18, 1]
+    width = 2 * H * dim + H * vdim + 5                                   # columns q | k | 5 others | v
+    rows = {i: rt(rng.normal(0, 1, (L + 6, width)), dtype) for i, L in enumerate(lens)}
+    slots = [2, 0, 3]
+    state = torch.full((4, H, dim, vdim), 7.0, device=DEV)               # what another request left behind
+    a = np.asarray(decay)
+    hi = a.astype(np.float32)
+    dhi, dlo = dev(hi), dev((a - hi.astype(np.float64)))
+    q_col, k_col, v_col = 0, H * dim, 2 * H * dim + 5
+
+    def split(x):
+        T = x.shape[0]
+        return (P.silu(x[:, :H * dim]).reshape(T, H, dim), P.silu(x[:, k_col:k_col + H * dim]).reshape(T, H, dim),
+                P.silu(x[:, v_col:v_col + H * vdim]).reshape(T, H, vdim))
+
+    want = {i: _plain_recurrence(*split(rows[i]), a)[0] for i in rows}
+    got = {i: np.zeros_like(want[i]) for i in rows}
+
+    def launch(pieces):
+        """pieces: (request, first row, rows)"""
+        x = np.concatenate([rows[i][p:p + n] for i, p, n in pieces])
+        cu = np.concatenate([[0], np.cumsum([n for _, _, n in pieces])])
+        o = torch.empty((x.shape[0], H * vdim), device=DEV)
+        K.lightning_scan(dev(x, dtype), q_col, k_col, v_col, dhi, dlo, state, i32(cu), i32([p for _, p, _ in pieces]),
+                         i32([slots[i] for i, _, _ in pieces]), o, len(pieces), H, dim, vdim, "silu", True)
+        o = o.cpu().double().numpy().reshape(-1, H, vdim)
+        for (i, p, n), r0 in zip(pieces, cu[:-1]):
+            got[i][p:p + n] = o[r0:r0 + n]
+
+    launch([(1, 0, cut[1])])
+    launch([(0, 0, cut[0]), (1, cut[1], lens[1] - cut[1]), (2, 0, 1)])
+    for s in range(6):                                                    # one-token steps, segments in another order
+        launch([(2, lens[2] + s, 1), (0, lens[0] + s, 1), (1, lens[1] + s, 1)])
+    tol = 2e-5 if dtype == torch.float32 else 2e-5                        # the inputs are the stored values on both sides
+    for i in rows:
+        scale = np.abs(want[i]).max()
+        assert np.abs(got[i] - want[i]).max() <= tol * max(scale, 1.0), (i, np.abs(got[i] - want[i]).max(), scale)
+
+
+def test_lightning_scan_a_far_key_counts_and_the_decay_does_not_drift():
+    """With a decay of 1 - 1e-4 over 3000 rows the first key's share is exp(-0.3); one key far back is made a hundred
+    times larger than the rest, so that losing it, or a decay rounded to float32 alone, shows in the last rows."""
+    from kappai_b200.ops import kernels as K
+    H, dim, vdim, T = 1, 8, 8, 3000
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 0.1, (T, 24))
+    x[3, 8:16] = 30.0                                                     # k of row 3
+    x[3, 16:24] = 30.0                                                    # v of row 3
+    a = np.array([1.0 - 1e-4])
+    q, k, v = (x[:, :8].reshape(T, 1, 8), x[:, 8:16].reshape(T, 1, 8), x[:, 16:].reshape(T, 1, 8))
+    want = _plain_recurrence(q, k, v, a)[0]
+    hi = a.astype(np.float32)
+    state = torch.zeros((1, H, dim, vdim), device=DEV)
+    o = torch.empty((T, 8), device=DEV)
+    # in three launches: rows 0..999, 1000..2499, then the rest
+    for r0, r1 in ((0, 1000), (1000, 2500), (2500, T)):
+        K.lightning_scan(dev(x[r0:r1]), 0, 8, 16, dev(hi), dev(a - hi.astype(np.float64)), state, i32([0, r1 - r0]), i32([r0]),
+                         i32([0]), o[r0:r1], 1, H, dim, vdim, None, True)
+    got = o.cpu().double().numpy().reshape(T, 1, 8)
+    assert np.abs(want[-1]).max() > 50 * np.abs(want[2]).max()            # the far key dominates the end
+    assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_wise_kernels(dtype):
+    from kappai_b200.ops import kernels as K
+    rng = np.random.default_rng(3)
+    n = 11
+    tol = 1e-5 if dtype == torch.float32 else 1.2e-2
+    # norms of two column stretches of a wider row
+    wide = rt(rng.normal(0, 2, (n, 61)), dtype)
+    w0, w1 = 1 + rng.normal(0, 0.2, 24), 1 + rng.normal(0, 0.2, 13)
+    o0, o1 = torch.empty((n, 24), dtype=dtype, device=DEV), torch.empty((n, 13), dtype=dtype, device=DEV)
+    K.rmsnorm_cols(dev(wide, dtype), [(3, dev(w0), o0), (40, dev(w1), o1)], 1e-5)
+    assert np.abs(o0.double().cpu().numpy() - P.rms_norm(wide[:, 3:27], w0, 1e-5)).max() <= tol * 3
+    assert np.abs(o1.double().cpu().numpy() - P.rms_norm(wide[:, 40:53], w1, 1e-5)).max() <= tol * 3
+    o1.zero_()
+    K.rmsnorm_cols(dev(wide, dtype), [(40, dev(w1), o1)], 1e-5)            # one stretch alone
+    assert np.abs(o1.double().cpu().numpy() - P.rms_norm(wide[:, 40:53], w1, 1e-5)).max() <= tol * 3
+    # norm of float32 rows times a sigmoid gate read from a wider row
+    o = rng.normal(0, 5, (n, 40))
+    g = rt(rng.normal(0, 2, (n, 50)), dtype)
+    w = 1 + rng.normal(0, 0.2, 40)
+    out = torch.empty((n, 40), dtype=dtype, device=DEV)
+    K.norm_gate_rows(dev(o), dev(w), dev(g, dtype)[:, 7:47], 1e-6, out)
+    assert np.abs(out.double().cpu().numpy() - P.rms_norm(o, w, 1e-6) * P.sigmoid(g[:, 7:47])).max() <= tol * 3
+    # the gate of the side input: act(gate) * a stretch of the token's row of a second table
+    gate, table = rt(rng.normal(0, 2, (n, 6)), dtype), rt(rng.normal(0, 1, (9, 30)), dtype)
+    ids = rng.integers(0, 9, n)
+    out = torch.empty((n, 6), dtype=dtype, device=DEV)
+    K.token_gate(dev(gate, dtype), dev(table, dtype), 12, i32(ids), out, "gelu_tanh")
+    assert np.abs(out.double().cpu().numpy() - P.gelu_tanh(gate) * table[ids][:, 12:18]).max() <= tol * 3
+    # x += norm(y) * w
+    x, y, w = rng.normal(0, 1, (n, 37)), rng.normal(0, 3, (n, 37)), 1 + rng.normal(0, 0.2, 37)
+    xd = dev(x)
+    K.rmsnorm_add_rows(dev(y), dev(w), 1e-5, xd)
+    assert np.abs(xd.double().cpu().numpy() - (x + P.rms_norm(y, w, 1e-5))).max() <= 1e-5
+    # out += sigmoid(h . wg) * y
+    h, wg = rt(rng.normal(0, 1, (n, 37)), dtype), rng.normal(0, 0.3, 37).astype(np.float32).astype(np.float64)
+    od = dev(x)
+    K.row_gate_add(dev(h, dtype), dev(wg), dev(y), od)
+    assert np.abs(od.double().cpu().numpy() - (x + P.sigmoid(h @ wg)[:, None] * y)).max() <= 2e-5
+    # the embedding with a scale and learned positions
+    emb, pos = rt(rng.normal(0, 1, (9, 20)), dtype), rt(rng.normal(0, 1, (50, 20)), dtype)
+    where = rng.integers(0, 50, n)
+    out = torch.empty((n, 20), device=DEV)
+    K.embed_rows(dev(emb, dtype), i32(ids), out, 3.0, dev(pos, dtype), i32(where))
+    assert np.abs(out.double().cpu().numpy() - (emb[ids] * 3.0 + pos[where])).max() <= 1e-6
+
+
+@pytest.mark.parametrize("M,K_,ff", [(4, 512, 256), (4, 96, 40), (100, 128, 64), (40, 1024, 512)])
+def test_tanh_gelu_in_the_gated_epilogues_of_the_products(M, K_, ff):
+    """Few rows with K a multiple of 512 stream their weights, other few-row shapes run the register kernel, many rows
+    run tcgen05: all three compute the tanh form of gelu on the gate themselves."""
+    from kappai_b200.ops.linear import linear_swiglu
+    rng = np.random.default_rng(M + ff)
+    a, w = rt(rng.normal(0, 1, (M, K_)), torch.bfloat16), rt(rng.normal(0, 1 / math.sqrt(K_), (2 * ff, K_)), torch.bfloat16)
+    got = linear_swiglu(dev(a, torch.bfloat16), dev(w, torch.bfloat16), None, "gelu_tanh").double().cpu().numpy()
+    g, u = rt(a @ w[:ff].T, torch.bfloat16), rt(a @ w[ff:].T, torch.bfloat16)
+    want = P.gelu_tanh(g) * u
+    assert np.abs(got - want).max() <= 0.02 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("n,E,ident,top,d", [(7, 5, 1, 2, 64), (130, 8, 2, 4, 128), (3, 3, 2, 5, 36), (40, 4, 0, 1, 48),
+                                             (9, 40, 3, 6, 50)])
+def test_router_over_all_scores_with_a_correction(n, E, ident, top, d):
+    """Both forms of the router (fused, and logits from a product) against the plain choice: the experts, in order, and
+    their weights; the layout gives identity experts places but no tiles."""
+    from kappai_b200.ops import kernels as K
+    rng = np.random.default_rng(n + E)
+    EA = E + ident
+    h = rt(rng.normal(0, 1, (n, d)), torch.bfloat16)
+    wr = rt(rng.normal(0, 3 / math.sqrt(d), (EA, d)), torch.bfloat16)
+    corr = rt(rng.normal(0, 0.05, EA), torch.bfloat16)
+    idx_w, wts_w, _ = P.route(h, wr, corr, top, 2.5)
+    for form in ("fused", "product"):
+        idx = torch.empty((n, top), dtype=torch.int32, device=DEV)
+        wts = torch.empty((n, top), device=DEV)
+        layout = torch.empty(K.moe_layout_ints(n, EA, top), dtype=torch.int32, device=DEV)
+        if form == "fused":
+            if not K.moe_router_ok(d, EA):
+                continue
+            K.moe_router(dev(h, torch.bfloat16), dev(wr), dev(corr), top, idx, wts, layout, routing="softmax_all", scale=2.5,
+                         n_identity=ident)
+        else:
+            K.moe_route(dev(h @ wr.T), top, idx, wts, layout, bias=dev(corr), routing="softmax_all", scale=2.5, n_identity=ident)
+        assert np.array_equal(idx.cpu().numpy(), idx_w), form
+        assert np.abs(wts.cpu().numpy() - wts_w).max() <= 2e-6, form
+        lay = layout.cpu().numpy()
+        offsets, tile_start = lay[:EA + 1], lay[EA + 1:2 * (EA + 1)]
+        counts = np.bincount(idx_w.reshape(-1), minlength=EA)
+        assert np.array_equal(np.diff(offsets), counts)
+        assert np.array_equal(np.diff(tile_start), np.where(np.arange(EA) < E, -(-counts // 32), 0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,E,ident,top,d,ff,shared", [(6, 5, 1, 2, 64, 24, 40), (300, 8, 2, 3, 128, 64, 128), (5, 3, 2, 5, 36, 20, 28),
+                                                       (33, 4, 0, 1, 48, 32, None)])
+def test_mixture_part_with_identity_and_shared_experts(n, E, ident, top, d, ff, shared, dtype):
+    from kappai_b200.config import PartSpec
+    from kappai_b200.parts import make_part
+    from test_parts_gpu import bind_random, env_for
+    rng = np.random.default_rng(n)
+    params = {"hidden_size": d, "expert_size": ff, "num_experts": E, "top": top, "activation": "silu", "routing": "softmax_all",
+              "router_scale": 1.7, "identity_experts": ident}
+    if shared:
+        params.update(shared_size=shared, shared_gate="sigmoid")
+    part = make_part("feed_forward", PartSpec("moe", params), env_for(dtype))
+    w = bind_random(part, rng, dtype)
+    part.w_router.mul_(3.0)
+    w["router.weight"] = w["router.weight"] * 3.0
+    h = rt(rng.normal(0, 1, (n, d)), dtype)
+    # rows whose choice is too close for 16-bit sums to call are left out of the comparison
+    ok = P.choice_margin(h, w["router.weight"], w["router.correction"], top) > (1e-5 if dtype == torch.float32 else 2e-3)
+    experts = [(w[f"experts.{e}.gate_proj.weight"], w[f"experts.{e}.up_proj.weight"], w[f"experts.{e}.down_proj.weight"]) for e in range(E)]
+    sh = None
+    if shared:
+        sh = (w["shared.gate_proj.weight"], w["shared.up_proj.weight"], w["shared.down_proj.weight"], w["shared.gate.weight"])
+    want = P.mixture(h, w["router.weight"], w["router.correction"], experts, ident, top, 1.7, sh)
+    res = torch.zeros((n, d), device=DEV)
+    part.forward(dev(h, dtype), res, None)
+    got = res.double().cpu().numpy()
+    tol = 2e-5 if dtype == torch.float32 else 0.03
+    assert ok.sum() >= n // 2
+    assert np.abs(got[ok] - want[ok]).max() <= tol * max(1.0, np.abs(want).max())
+
+
+def _latent_params(H, dim, vdim, qr, kvr, d, scale):
+    return {"hidden_size": d, "num_heads": H, "head_dim": dim, "value_dim": vdim, "q_rank": qr, "kv_rank": kvr, "scale": scale,
+            "norm_eps": 1e-5, "gate": "sigmoid", "softmax_weights": "float32"}
+
+
+def _plain_latent(w, h, H, dim, vdim, scale):
+    names = {"dq": "q_down.weight", "dq.norm": "q_norm.weight", "uq": "q_up.weight", "dkv": "kv_down.weight",
+             "dkv.norm": "kv_norm.weight", "uk": "k_up.weight", "uv": "v_up.weight", "g": "gate_proj.weight", "o": "out_proj.weight"}
+    return P.latent_attention(h, {k: w[v] for k, v in names.items()}, H, dim, vdim, scale, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dim,vdim,qr,kvr,d,page,scale", [
+    (4, 16, 16, 24, 40, 64, 16, 0.25), (3, 24, 8, 16, 16, 48, 8, 0.2), (2, 12, 20, 12, 20, 36, 32, 0.3),
+    (2, 64, 64, 32, 48, 128, 64, 0.125), (2, 128, 128, 64, 96, 256, 64, 0.09), (5, 8, 8, 20, 12, 40, 16, 3.0)])
+def test_latent_attention_part_in_batches_cut_in_two(H, dim, vdim, qr, kvr, d, page, scale, dtype):
+    """Three requests, each in two steps (all in one batch), one of them a single token then the rest; keys lie on
+    both sides of page borders and of the 256-key chunks.  The last case has a scale so large that a row's
+    softmax sits on one key, often far back: a key that is one off shows."""
+    from kappai_b200.config import PartSpec
+    from kappai_b200.parts import make_part
+    from test_parts_gpu import bind_random, env_for, run_mixer_two_steps
+    rng = np.random.default_rng(H * dim)
+    part = make_part("mixer", PartSpec("latent_attention", _latent_params(H, dim, vdim, qr, kvr, d, scale)), env_for(dtype, 1024))
+    w = bind_random(part, rng, dtype)
+    lens, cuts = [300, 70, 33], [1, 64, 31]
+    hs = [rt(rng.normal(0, 1, (L, d)), dtype) for L in lens]
+    outs = run_mixer_two_steps(part, hs, lens, cuts, page, dtype)
+    for h, got in zip(hs, outs):
+        want = _plain_latent(w, h, H, dim, vdim, scale)
+        tol = 3e-5 if dtype == torch.float32 else (0.05 if scale < 1 else 0.35)
+        err = np.abs(got - want).max() / max(1.0, np.abs(want).max())
+        assert err <= tol, err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,dim,vdim,d,decay", [(2, 16, 32, 64, [0.9, 0.995]), (3, 40, 24, 48, [0.3, 1.0, 0.999]),
+                                               (4, 64, 64, 256, [0.6, 0.9, 0.99, 0.999]), (2, 128, 64, 128, [0.97, 1.0])])
+def test_lightning_part_in_batches_cut_in_two(H, dim, vdim, d, decay, dtype):
+    from kappai_b200.config import PartSpec
+    from kappai_b200.parts import make_part
+    from test_parts_gpu import bind_random, env_for, run_mixer_two_steps
+    rng = np.random.default_rng(H + dim)
+    params = {"hidden_size": d, "num_heads": H, "head_dim": dim, "value_dim": vdim, "decay": decay, "norm_eps": 1e-5}
+    part = make_part("mixer", PartSpec("lightning", params), env_for(dtype, 1024))
+    w = bind_random(part, rng, dtype)
+    lens, cuts = [300, 70, 33], [1, 64, 31]
+    hs = [rt(rng.normal(0, 1, (L, d)), dtype) for L in lens]
+    outs = run_mixer_two_steps(part, hs, lens, cuts, 16, dtype)
+    for h, got in zip(hs, outs):
+        want = P.lightning(h, w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"], w["gate_proj.weight"], w["out_proj.weight"],
+                           w["norm.weight"], decay, H, dim, vdim, 1e-5)[0]
+        tol = 3e-5 if dtype == torch.float32 else 0.05
+        err = np.abs(got - want).max() / max(1.0, np.abs(want).max())
+        assert err <= tol, err
+
+
+# ------------------------------------------------------------------------------------------ whole models
+
+# The smallest gap between a chosen and an unchosen router output (in choice score) that a request's tokens may have.
+# In 16 bits a row's router inputs differ from the plain ones by about half a per cent and its scores by a few 1e-3, so a
+# closer call may fall the other way, and the token that took another expert stays in the states and caches behind
+# it.  Requests grow four tokens at a time, and four tokens that bring a closer call are drawn again.  (The bound is
+# wider where fewer experts share the scores: one expert of four has a weight of a half, three of ten a tenth each.)
+MARGINS = {"A": 0.006, "B": 0.012, "C": 0.01, "D": 0.001, "E": 0.008}
+LENGTHS = {"A": [70, 3, 121, 49], "B": [90, 41, 2, 130], "C": [77, 20, 101], "D": [260, 64, 150], "E": [150, 65, 140]}
+PROMPTS = {"A": [30, 1, 60, 48], "B": [50, 40, 1, 100], "C": [40, 19, 60], "D": [230, 3, 101], "E": [100, 64, 30]}
+BF16_REL_RMS = 0.04    # bound on a row's 16-bit error (rms over the vocabulary / the row's spread) for 95 % of the rows
+BF16_WORST = 0.2       # ... and for all but one row in a hundred (a router call that fell the other way after all): the
+                       # second to fifth position of a sequence err most (measured: 13 % at the second, 6 % at the third),
+                       # because a mixer's output there is a sum of two or three terms, each a product of three rounded
+                       # factors, where later positions average over many
+BF16_BETWEEN_CUTS = 0.1    # bound on the same measure between two cuts' rows of one position, again for 99 in a hundred
+_PLAIN = {}
+_REQS = {}
+
+
+def _requests(plain, name, lengths, seed, margin=None):
+    """Random requests whose router choices all have a margin (``MARGINS``; see there)."""
+    margin = MARGINS[name] if margin is None else margin
+    key = (name, tuple(lengths), seed, margin)
+    if key in _REQS:
+        return _REQS[key]
+    rng = np.random.default_rng(seed)
+    reqs = {}
+    for i, n in enumerate(lengths):
+        toks = []
+        while len(toks) < n:
+            new = rng.integers(0, plain.cfg["vocab"], min(4, n - len(toks))).tolist()
+            m = []
+            plain.forward(toks + new, margins=m)
+            if m and min(float(x[len(toks):].min()) for x in m) < margin:
+                continue
+            toks += new
+        reqs[f"r{i}"] = toks
+    _REQS[key] = reqs
+    return reqs
+
+
+def _expect(plain, name, toks):
+    """(the plain logits [T, vocab], every position's smallest router margin [T]) of a sequence."""
+    key = (name, tuple(toks))
+    if key not in _PLAIN:
+        m = []
+        lg = plain.forward(toks, margins=m)
+        _PLAIN[key] = (lg, np.min(m, axis=0) if m else np.full(len(toks), np.inf))
+    return _PLAIN[key]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("A", 16), ("B", None), ("C", 32), ("D", None), ("E", 8)])
+def test_every_cut_agrees_with_plain(name, page_size, dtype, vek_dirs, vek_plain, tmp_path):
+    """Whole prompts, the last tokens decoded one by one, portions down to two tokens, and up to four requests mixed
+    in a pool so small that pages and slots go round."""
+    plain = vek_plain[name]
+    reqs = _requests(plain, name, LENGTHS[name], 31)
+    prompt_len = dict(zip(reqs, PROMPTS[name]))
+    expected = {rid: _expect(plain, name, t)[0] for rid, t in reqs.items()}
+    page = page_size or 64
+    rounded = sorted(-(-len(t) // page) * page for t in reqs.values())
+    max_tokens = rounded[-1] + rounded[0] + 2 * page          # the longest request and the shortest fit together, not all
+    tr = R.Trace()
+    R.whole(tr, reqs)
+    R.last_decoded(tr, reqs, n_last=60)
+    R.portions(tr, reqs)
+    b = len(tr.steps)
+    R.mixed(tr, reqs, prompt_len, seed=5, max_live=4, page=page, max_tokens=max_tokens)
+    assert max(len(s["entries"]) for s in tr.steps[b:]) >= 2
+    out = R.run_trace(vek_dirs[name], dtype, tr, str(tmp_path / "out"), max_tokens, page_size)
+    rel = []
+    for st, rows in zip(tr.steps, tr.rows):
+        for j, (rid, pos) in enumerate(rows):
+            e = expected[rid][pos]
+            rel.append((float(np.sqrt(np.mean((out[st["step"]][j] - e) ** 2)) / e.std()), st["step"], rid, pos))
+    r = np.array([x[0] for x in rel])
+    print(f"{name} {dtype}: relative rms error median {np.median(r):.2e}, 95 % {np.quantile(r, 0.95):.2e}, worst {r.max():.2e}")
+    if dtype == "bfloat16":
+        # rounding alone gives a few per cent (these weights have unit gain: every sublayer moves the residual); a
+        # wrong key, a lost state, a wrong page or expert gives tens
+        assert np.quantile(r, 0.95) <= BF16_REL_RMS and np.quantile(r, 0.99) <= BF16_WORST, max(rel)
+        apart = []
+        for place, rows in R.rows_by_place(tr, out).items():
+            e = expected[place[0]][place[1]]
+            apart.append(max(float(np.sqrt(np.mean((x - rows[0]) ** 2)) / e.std()) for x in rows[1:]))
+        assert np.quantile(apart, 0.99) <= BF16_BETWEEN_CUTS, max(apart)
+    else:
+        assert r.max() <= 1e-4, max(rel)
+    stats = R.cache_stats(str(tmp_path / "out"))
+    assert stats and all(g["reused"] > 0 and g["handed_out"] > g["pages"] for g in stats.values()), stats
+    if dtype == "float32":
+        for place, rows in R.rows_by_place(tr, out).items():
+            assert len(rows) >= 2, place
+            for x in rows[1:]:
+                assert np.array_equal(rows[0], x), f"{name}: float32 logits of {place} differ between cuts"
+
+
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+def test_residual_after_every_layer_run(name, vek_dirs, vek_plain):
+    from kappai_b200 import ModelRunner, StepEntry
+    plain = vek_plain[name]
+    toks = _requests(plain, name, [57], 8, 1e-5)["r0"]
+    want = []
+    plain.forward(toks, want)
+    r = ModelRunner(vek_dirs[name], dtype="float32", max_tokens=256, max_requests=2, cuda_graphs=False)
+    got = []
+    r.observer = lambda i, x: got.append(x.detach().cpu().numpy().copy())
+    r.step([StepEntry("a", toks, [0])])
+    assert len(got) == len(want) + 1 == len(P.layer_runs(plain.cfg)) + 1
+    for i, w in enumerate(want):
+        assert np.abs(got[i + 1] - w).max() < 1e-4 * max(1.0, np.abs(w).max()), (i, np.abs(got[i + 1] - w).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batched_requests_equal_each_alone_and_captured_steps_equal_eager(dtype, vek_dirs, vek_plain):
+    """Unequal requests decode together for many steps (the steps are captured into CUDA graphs on the way); every
+    row equals the row of the request run alone without graphs."""
+    from kappai_b200 import ModelRunner, StepEntry
+    plain = vek_plain["A"]
+    n_dec = 40
+    reqs = _requests(plain, "A", [61 + n_dec, 9 + n_dec, 30 + n_dec], 12)
+
+    def run(runner, group):
+        out = {rid: [] for rid in group}
+        lg = runner.step([StepEntry(rid, reqs[rid][:len(reqs[rid]) - n_dec], [len(reqs[rid]) - n_dec - 1]) for rid in group])
+        for j, rid in enumerate(group):
+            out[rid].append(lg[j].cpu().numpy().copy())
+        for s in range(n_dec):
+            lg = runner.step([StepEntry(rid, [reqs[rid][len(reqs[rid]) - n_dec + s]], [0]) for rid in group])
+            for j, rid in enumerate(group):
+                out[rid].append(lg[j].cpu().numpy().copy())
+        for rid in group:
+            runner.end(rid)
+        return out
+
+    r1 = ModelRunner(vek_dirs["A"], dtype=dtype, max_tokens=512, max_requests=4, page_size=16)
+    together = run(r1, list(reqs))
+    assert r1.model.graph_safe and r1.graphs is not None and len(r1.graphs.graphs) >= 1
+    alone_runner = ModelRunner(vek_dirs["A"], dtype=dtype, max_tokens=512, max_requests=4, page_size=16, cuda_graphs=False)
+    for rid in reqs:
+        alone = run(alone_runner, [rid])[rid]
+        for a, b in zip(alone, together[rid]):
+            if dtype == "float32":
+                assert np.array_equal(a, b)
+            else:
+                assert np.abs(a - b).max() <= 2 * tol_for(dtype, a)
+
+
+def test_a_slot_used_again_starts_from_an_empty_state(vek_dirs):
+    """One slot: a second request takes the slot (and the pages) of the first and gives what it gives alone."""
+    from kappai_b200 import ModelRunner, StepEntry
+    rng = np.random.default_rng(2)
+    a, b = rng.integers(0, 211, 40).tolist(), rng.integers(0, 211, 25).tolist()
+    r = ModelRunner(vek_dirs["A"], dtype="float32", max_tokens=64, max_requests=1, page_size=16, cuda_graphs=False)
+    r.step([StepEntry("a", a, [len(a) - 1])])
+    r.end("a")
+    second = r.step([StepEntry("b", b[:7], [6])]).cpu().numpy().copy()
+    second2 = r.step([StepEntry("b", b[7:], [len(b) - 8])]).cpu().numpy().copy()
+    r.end("b")
+    fresh = ModelRunner(vek_dirs["A"], dtype="float32", max_tokens=64, max_requests=1, page_size=16, cuda_graphs=False)
+    assert np.array_equal(second, fresh.step([StepEntry("x", b[:7], [6])]).cpu().numpy())
+    assert np.array_equal(second2, fresh.step([StepEntry("x", b[7:], [len(b) - 8])]).cpu().numpy())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_engine(name, dtype, vek_dirs, vek_plain):
+    from kappai_b200 import Engine, EngineArgs, SamplingParams
+    plain = vek_plain[name]
+    prompts = list(_requests(plain, name, [5, 26, 60], 21, 1e-5).values())
+    n_new = 50
+    eng = Engine(EngineArgs(model=vek_dirs[name], dtype=dtype, max_batch=4, max_step_tokens=16, page_size=16, kv_tokens=1024))
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, n_predict=n_new))
+    assert [len(o) for o in outs] == [n_new] * len(prompts)
+    for p, o in zip(prompts, outs):
+        lg, margin = _expect(plain, name, p + o)
+        lg, margin = lg[len(p) - 1:-1], margin[len(p) - 1:-1]
+        for j, t in enumerate(o):
+            if dtype == "bfloat16" and margin[:j + 1].min() < MARGINS[name]:
+                break                                                 # a router choice too close for 16 bits to call
+            best = int(np.argmax(lg[j]))
+            assert t == best or lg[j][best] - lg[j][t] <= 4 * tol_for(dtype, lg[j]), (j, t, best)
+    assert eng.runner.cache.slots.n_free == 4 and all(p.n_free == p.n_pages for p in eng.runner.cache.pools.values())
+
+
+def test_command_line_and_random_weights(vek_dirs, vek_plain, tmp_path):
+    """The command line runs the design like any other: greedy tokens equal the plain model's, --time names the
+    design's kernels, and --random-weights writes a loadable model folder from a Vekuzen config.json."""
+    import json
+    import os
+    import subprocess
+    import sys
+    plain = vek_plain["A"]
+    prompt = _requests(plain, "A", [30], 77, 1e-5)["r0"]
+    cmd = [sys.executable, "-m", "kappai_b200.cli", "-m", vek_dirs["A"], "-p", ",".join(map(str, prompt)), "-n", "12", "-t", "0",
+           "--fp32", "--time"]
+    p = subprocess.run(cmd, cwd=R.ROOT, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(t) for t in p.stdout.split()]
+    assert len(out) == 12
+    lg = plain.forward(prompt + out)[len(prompt) - 1:-1]
+    for j, t in enumerate(out):
+        best = int(np.argmax(lg[j]))
+        assert t == best or lg[j][best] - lg[j][t] <= 1e-4, (j, t, best)
+    for name in ("lightning_scan", "norm_gate_rows", "rmsnorm_cols", "moe_router", "moe_experts", "token_gate", "rmsnorm_add_rows",
+                 "row_gate_add", "attention_split"):
+        assert name in p.stderr, (name, p.stderr[-3000:])
+    cfgp = tmp_path / "c.json"
+    cfgp.write_text(json.dumps(CONFIGS["C"][0]))
+    made = tmp_path / "rw"
+    cmd = [os.path.join(R.ROOT, "bin", "kappai-cli"), "--random-weights", str(cfgp), "-s", "5", "-m", str(made), "-t", "0", "-n", "5",
+           "1 2 3"]
+    p = subprocess.run(cmd, cwd=str(tmp_path), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len(p.stdout.split()) == 5 and os.path.isfile(made / "model.safetensors")
