@@ -37,6 +37,11 @@ random weights, beside an LFM2 model of attention layers of the same sizes: one 
 and decode steps of ``--batch`` requests at a context of about 2,048, on the device, and the device time of
 both steps by kernel class.  It prints a line of its own; the default line is unchanged.
 
+``--design vekuzen`` does the same for the Vekuzen design (pre-norm layers of latent attention and of linear
+attention with decay, tanh-gelu gated units and mixtures with identity and shared experts, a looped stretch of
+layers, learned positions, per-layer token inputs) beside a Tizusun model of the same layer sizes, the closest
+design the engine has (gated attention, dense and mixture feed-forwards, whole softmax weights).
+
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and
 exits with 2.
 """
@@ -409,6 +414,28 @@ def tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers):
             "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": dict(dense if c == "d" else moe)} for c in layers]}
 
 
+VEKUZEN_POSITIONS = 4096
+
+
+def vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers):
+    """Layers of the same sizes as the other designs' (``layers``: d = dense, m = mixture): latent attention and
+    lightning layers in turn, the mixtures with two identity experts and a shared unit of an expert's size, the
+    middle layers a loop that runs once, side inputs of 256 columns."""
+    latent = {"heads": H, "dim": hd, "vdim": hd, "q_rank": max(512, width // 2), "kv_rank": 512, "scale": hd ** -0.5}
+    light = {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-3 - 6 * h / max(1, H - 1)) for h in range(H)]}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff_e}, "router": {"experts": E, "identity": 2, "top": top, "scale": 2.5},
+           "shared": {"ff": ff_e}}
+    n = len(layers)
+    cfg = {"architecture": "Vekuzen", "vocab": DESIGN_VOCAB, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+           "logit_scale": 1.0, "max_positions": VEKUZEN_POSITIONS, "token_side": {"dim": 256},
+           "layers": [{"type": "latent_attention" if i % 2 == 0 else "lightning", "mixer": dict(latent if i % 2 == 0 else light),
+                       "mlp": dict(dense if c == "d" else moe)} for i, c in enumerate(layers)]}
+    if n >= 3:
+        cfg["loop"] = {"start": 1, "stop": n - 1, "times": 1}
+    return cfg
+
+
 def lfm2_like_config(width, H, G, hd, ff, n_layers):
     return dict(architectures=["Lfm2ForCausalLM"], vocab_size=DESIGN_VOCAB, hidden_size=width, num_hidden_layers=n_layers,
                 num_attention_heads=H, num_key_value_heads=G, head_dim=hd, layer_types=["full_attention"] * n_layers,
@@ -453,12 +480,15 @@ def run_design(a) -> int:
     from kappai_b200 import ModelRunner, StepEntry
 
     import kappai_b200.models.tizusun as tz
-    tz.SOFTMAX_WEIGHTS = a.softmax_weights
+    import kappai_b200.models.vekuzen as vk
+    tz.SOFTMAX_WEIGHTS = vk.SOFTMAX_WEIGHTS = a.softmax_weights
     pk = peaks()
     T, B, ctx_len = PROMPT_LEN, a.batch, PROMPT_LEN + 256
     warmup = max(a.warmup, 3)
     steps = min(a.steps, 128)
-    out = {"design": "Tizusun", "beside": "LFM2 attention layers of the same sizes", "dtype": "bf16",
+    vekuzen = a.design == "vekuzen"
+    out = {"design": "Vekuzen" if vekuzen else "Tizusun",
+           "beside": "Tizusun layers of the same sizes" if vekuzen else "LFM2 attention layers of the same sizes", "dtype": "bf16",
            "softmax_weights": a.softmax_weights,
            "data": "synthetic: random weights, uniform random token ids", "prompt_tokens": T, "decode_batch": B,
            "decode_context": f"{T} to {ctx_len}", "peaks": pk, "sizes": {}}
@@ -468,8 +498,11 @@ def run_design(a) -> int:
         if a.size and a.size != name:
             continue
         rec = {}
-        for model, cfg in (("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers)),
-                           ("lfm2", lfm2_like_config(width, H, G, hd, ff, len(layers)))):
+        pair = ((("vekuzen", vekuzen_config(width, H, G, hd, ff, E, top, ff_e, layers)),
+                 ("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers))) if vekuzen else
+                (("tizusun", tizusun_config(width, H, G, hd, ff, E, top, ff_e, layers)),
+                 ("lfm2", lfm2_like_config(width, H, G, hd, ff, len(layers)))))
+        for model, cfg in pair:
             rng = np.random.default_rng(SEED)
             runner = ModelRunner(folder_for(cfg, SEED), dtype="bfloat16", max_tokens=(B + 1) * (ctx_len + 64), max_requests=B + 1,
                                  page_size=64, max_model_len=ctx_len + 64)
@@ -612,12 +645,13 @@ def main() -> int:
                     help="with --workload: launch every kernel on its own between CUDA events and print the device "
                          "time by kernel class (the run's throughput is then not the engine's)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
-    ap.add_argument("--design", choices=["tizusun"], default=None,
-                    help="time another design at a few layer sizes beside LFM2 attention layers of the same sizes "
+    ap.add_argument("--design", choices=["tizusun", "vekuzen"], default=None,
+                    help="time another design at a few layer sizes beside the closest existing model of the same sizes "
+                         "(tizusun beside LFM2 attention layers, vekuzen beside tizusun) "
                          "(prefill, decode, device time by kernel class) instead of the default line")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only (e.g. 2048x32h64)")
     ap.add_argument("--softmax-weights", choices=["float32", "operand"], default="float32",
-                    help="with --design tizusun: how the softmax weights meet the values: whole (the design's way: the "
+                    help="with --design: how the softmax weights meet the values: whole (the design's way: the "
                          "mma.sync kernels multiply their three bfloat16 parts) or rounded to one bfloat16 operand (the "
                          "tcgen05 prompt kernel can then run)")
     a = ap.parse_args()

@@ -12,7 +12,11 @@ side by side are RMS-normed as one row with a weight, multiplied by
 state is the request's only memory of this mixer: float32, one slot a request,
 zero at position 0.  The four matrices that read the layer's input run as one
 product; the recurrence, the norm and the gate are float32 (csrc/lightning.cu,
-``norm_gate_rows``).
+``norm_gate_rows``).  Decoded tokens and short portions run the scan kernel
+(row after row, the same bits however a sequence is cut; the 32-bit mode runs
+it always); in 16-bit mode a step with a portion of ``CHUNKED_FROM`` rows or
+more runs the chunked kernel (the rows of a chunk as small float32 matrix
+products).
 
 Params: hidden_size, num_heads, head_dim, value_dim, decay (a list, one a
 head), norm_eps, activation ("silu" | None), gate ("sigmoid").
@@ -29,6 +33,9 @@ from ..config.schema import ConfigError
 from ..ops import kernels as K
 from ..ops.linear import linear
 from .base import Part, WeightSpec, register_part
+
+
+CHUNKED_FROM = 16      # rows of a step's longest segment from which the chunked kernel runs (16-bit mode)
 
 
 class LightningAttention(Part):
@@ -73,6 +80,11 @@ class LightningAttention(Part):
         dev = self.w_in.device
         self.decay_hi = torch.from_numpy(hi).to(dev)
         self.decay_lo = torch.from_numpy(lo).to(dev)
+        # the chunked kernel's table of powers a^0 .. a^rows, made in double
+        self.decay_pow = None
+        if dev.type == "cuda" and self.env.dtype != torch.float32 and self.dim <= K.LIGHTNING_CHUNK_MAX_DIM:
+            m = np.arange(K.lightning_chunk_rows() + 1, dtype=np.float64)
+            self.decay_pow = torch.from_numpy(np.power(a[:, None], m[None, :]).astype(np.float32)).contiguous().to(dev)
 
     def cache_spec(self):
         return StateSpec((self.H, self.dim, self.vdim), "float32")
@@ -82,8 +94,12 @@ class LightningAttention(Part):
         H, dim, vdim, n = self.H, self.dim, self.vdim, ctx.n_rows
         p = linear(h, self.w_in)                                 # [q | k | v | gate]
         o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
-        K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows, ctx.seg_pos,
-                         ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
+        if self.decay_pow is not None and ctx.max_seg_len >= CHUNKED_FROM:
+            K.lightning_chunked(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos,
+                                ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
+        else:
+            K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows, ctx.seg_pos,
+                             ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
         g0 = 2 * H * dim + H * vdim
         og = torch.empty((n, H * vdim), dtype=p.dtype, device=p.device)
         K.norm_gate_rows(o, self.norm_w, p[:, g0:g0 + H * vdim], self.eps, og)
