@@ -8,7 +8,7 @@
 // thousand steps of it do not drift from the constant the model gives), the products and the sums.  The state of a
 // request lives in its slot between steps and counts as zero at position 0.
 //
-// Two kernels.  The scan: a block walks the rows of one (segment, head, 16 value columns) in order, the state in
+// Three forms.  The scan: a block walks the rows of one (segment, head, 16 value columns) in order, the state in
 // registers (thread = (value column, a sixteenth of the key rows)); rows are staged 16 (or 8) at a time, q and k with
 // their activation applied once, and a thread reads its stretch of them as float4.  One row a segment is the decode
 // step.  Every sum has a fixed order that depends on the head's size alone, so a row's bits do not depend on how the
@@ -20,6 +20,9 @@
 // three small float32 matrix products from shared memory (q and k staged transposed, so that every product reads
 // its operands along rows) instead of LC_C dependent steps.  The powers of the decay come from a table made in
 // double on the host.  Sums have another order than the scan's, so the 32-bit mode keeps the scan.
+//
+// The chunks in parallel, for steps of few segments (one long prompt): the same products with the chunks of all
+// segments side by side and a short serial pass between them (see "chunks in parallel" below).
 #include "common.cuh"
 
 #define LT_CH_MAX 16             // rows staged at a time by the scan (half as many for the largest heads: shared memory)
@@ -330,6 +333,213 @@ lightning_chunked_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col
     }
 }
 
+
+// ------------------------------------------------------------------------------------------ chunks in parallel
+// The chunked form with the chunks of all segments side by side (a list built on the host: chunk -> segment, first
+// row): (1) every chunk's own sum U_c = sum_j a^(n-1-j) k_j v_j^T, all chunks at once; (2) a short serial pass a
+// (segment, head) turns the sums into the states at the chunks' heads, S_(c+1) = a^n S_c + U_c, in place, and leaves
+// the segment's last state in its slot; (3) every chunk's outputs from its state and its own rows, all chunks at once.
+// The products are those of the kernel above; only (2) is serial, and it is one multiply-add an element and chunk.
+
+// A [rows t0 .. t0 + n) x [dim] stretch of columns, with the activation, transposed into dst [dim][LC_LD]
+// (zeros behind the n rows).
+template <typename T, int ACT, bool VEC>
+__device__ __forceinline__ void lc_stage_transposed(float* dst, const T* __restrict__ qkv, int ld, int col, int head, int dim,
+                                                    int t0, int n, int tid) {
+    if (VEC) {
+        const int ng = dim / 8;
+        for (int x = tid; x < ng * LC_C; x += LC_THREADS) {
+            const int t = x % LC_C, g = x / LC_C;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (t < n) raw = __ldg(reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + t) * ld + col + head * dim + g * 8));
+            const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; e++) dst[(g * 8 + e) * LC_LD + t] = t < n ? lt_act<ACT>(__bfloat162float(e8[e])) : 0.f;
+        }
+    } else {
+        for (int x = tid; x < dim * LC_C; x += LC_THREADS) {
+            const int t = x % LC_C, d = x / LC_C;
+            dst[d * LC_LD + t] = t < n ? lt_act<ACT>(to_f32(qkv[(size_t)(t0 + t) * ld + col + head * dim + d])) : 0.f;
+        }
+    }
+}
+
+template <typename T, int ACT>
+__device__ __forceinline__ void lc_stage_values(float* Vs, const T* __restrict__ qkv, int ld, int v_col, int head, int vdim,
+                                                int tile, int t0, int n, int tid) {
+    for (int x = tid; x < LC_C * LC_COLS; x += LC_THREADS) {
+        const int t = x / LC_COLS, c = x % LC_COLS, j = tile * LC_COLS + c;
+        Vs[x] = (t < n && j < vdim) ? lt_act<ACT>(to_f32(qkv[(size_t)(t0 + t) * ld + v_col + head * vdim + j])) : 0.f;
+    }
+}
+
+// (1) U[chunk][head] = sum_j a^(n-1-j) k_j v_j^T
+template <typename T, int ACT, bool VEC>
+__global__ void __launch_bounds__(LC_THREADS)
+lightning_chunk_sums_kernel(const T* __restrict__ qkv, int ld, int k_col, int v_col, const float* __restrict__ decay_pow,
+                            const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg,
+                            const int* __restrict__ chunk_row0, float* __restrict__ U, int H, int dim, int vdim) {
+    kp_pdl_begin();
+    extern __shared__ __align__(16) float lc_sm[];
+    float* Kt = lc_sm;                                           // [dim][LC_LD]
+    float* Vs = Kt + (size_t)dim * LC_LD;                        // [LC_C][LC_COLS]
+    float* kw = Vs + LC_C * LC_COLS;                             // [LC_C]
+    const int chunk = blockIdx.x, head = blockIdx.y, tile = blockIdx.z, tid = threadIdx.x;
+    const int t0 = chunk_row0[chunk], n = min(LC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
+    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid);
+    lc_stage_values<T, ACT>(Vs, qkv, ld, v_col, head, vdim, tile, t0, n, tid);
+    for (int x = tid; x < LC_C; x += LC_THREADS) kw[x] = x < n ? decay_pow[(size_t)head * (LC_C + 1) + n - 1 - x] : 0.f;
+    __syncthreads();
+    const int r0 = (tid / 8) * 2, c0 = (tid % 8) * 4;
+    float* Uc = U + ((size_t)chunk * H + head) * dim * vdim;
+    for (int d0 = r0; d0 < dim; d0 += 2 * (LC_THREADS / 8)) {
+        float acc[2][4];
+#pragma unroll
+        for (int a = 0; a < 2; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+        const bool two = d0 + 1 < dim;
+#pragma unroll 4
+        for (int j = 0; j < n; j++) {
+            const float w = kw[j];
+            const float k0 = Kt[d0 * LC_LD + j] * w, k1 = two ? Kt[(d0 + 1) * LC_LD + j] * w : 0.f;
+            const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * LC_COLS + c0);
+            acc[0][0] = fmaf(k0, v4.x, acc[0][0]); acc[0][1] = fmaf(k0, v4.y, acc[0][1]);
+            acc[0][2] = fmaf(k0, v4.z, acc[0][2]); acc[0][3] = fmaf(k0, v4.w, acc[0][3]);
+            acc[1][0] = fmaf(k1, v4.x, acc[1][0]); acc[1][1] = fmaf(k1, v4.y, acc[1][1]);
+            acc[1][2] = fmaf(k1, v4.z, acc[1][2]); acc[1][3] = fmaf(k1, v4.w, acc[1][3]);
+        }
+#pragma unroll
+        for (int a = 0; a < 2; a++) {
+            if (d0 + a >= dim) continue;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int j = tile * LC_COLS + c0 + b;
+                if (j < vdim) Uc[(size_t)(d0 + a) * vdim + j] = acc[a][b];
+            }
+        }
+    }
+}
+
+// (2) in place: U[chunk] <- the state at the chunk's head; the segment's slot <- the state behind its last chunk
+__global__ void __launch_bounds__(256)
+lightning_chunk_states_kernel(float* __restrict__ U, const float* __restrict__ decay_pow, float* __restrict__ state,
+                              const int* __restrict__ cu_rows, const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
+                              const int* __restrict__ seg_chunk0, const int* __restrict__ chunk_row0, int H, int dim, int vdim,
+                              int write_state) {
+    kp_pdl_begin();
+    const int seg = blockIdx.x, head = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= dim * vdim) return;
+    float* st = state + (((size_t)seg_slot[seg] * H + head) * dim) * vdim + e;
+    float S = seg_pos[seg] == 0 ? 0.f : *st;
+    const int row1 = cu_rows[seg + 1];
+    for (int c = seg_chunk0[seg]; c < seg_chunk0[seg + 1]; c++) {
+        const int n = min(LC_C, row1 - chunk_row0[c]);
+        float* p = U + ((size_t)c * H + head) * dim * vdim + e;
+        const float u = *p;
+        *p = S;
+        S = fmaf(decay_pow[(size_t)head * (LC_C + 1) + n], S, u);
+    }
+    if (write_state) *st = S;
+}
+
+// (3) o_i = sum_{j <= i} a^(i-j) (q_i . k_j) v_j + a^(i+1) q_i^T S, S the state at the chunk's head
+template <typename T, int ACT, bool VEC>
+__global__ void __launch_bounds__(LC_THREADS)
+lightning_chunk_out_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay_pow,
+                           const int* __restrict__ cu_rows, const int* __restrict__ chunk_seg, const int* __restrict__ chunk_row0,
+                           const float* __restrict__ U, float* __restrict__ o, int ldo, int H, int dim, int vdim) {
+    kp_pdl_begin();
+    extern __shared__ __align__(16) float lc_sm[];
+    float* Qt = lc_sm;                                           // [dim][LC_LD]
+    float* Kt = Qt + (size_t)dim * LC_LD;                        // [dim][LC_LD]
+    float* Vs = Kt + (size_t)dim * LC_LD;                        // [LC_C][LC_COLS]
+    float* Ps = Vs + LC_C * LC_COLS;                             // [LC_C][LC_LD]
+    float* Ss = Ps + LC_C * LC_LD;                               // [dim][LC_COLS]
+    float* pw = Ss + (size_t)dim * LC_COLS;                      // [LC_C + 1]
+    const int chunk = blockIdx.x, head = blockIdx.y, tile = blockIdx.z, tid = threadIdx.x;
+    const int t0 = chunk_row0[chunk], n = min(LC_C, cu_rows[chunk_seg[chunk] + 1] - t0);
+    lc_stage_transposed<T, ACT, VEC>(Qt, qkv, ld, q_col, head, dim, t0, n, tid);
+    lc_stage_transposed<T, ACT, VEC>(Kt, qkv, ld, k_col, head, dim, t0, n, tid);
+    lc_stage_values<T, ACT>(Vs, qkv, ld, v_col, head, vdim, tile, t0, n, tid);
+    const float* Sc = U + ((size_t)chunk * H + head) * dim * vdim;
+    for (int x = tid; x < dim * LC_COLS; x += LC_THREADS) {
+        const int d = x / LC_COLS, c = x % LC_COLS, j = tile * LC_COLS + c;
+        Ss[x] = j < vdim ? Sc[(size_t)d * vdim + j] : 0.f;
+    }
+    for (int x = tid; x <= LC_C; x += LC_THREADS) pw[x] = decay_pow[(size_t)head * (LC_C + 1) + x];
+    __syncthreads();
+    const int i0 = (tid / 16) * 4, j0 = (tid % 16) * 4;
+    const int r0 = (tid / 8) * 2, c0 = (tid % 8) * 4;
+    {
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
+        if (j0 <= i0 + 3 && i0 < n) {
+#pragma unroll 4
+            for (int d = 0; d < dim; d++) {
+                const float4 q4 = *reinterpret_cast<const float4*>(Qt + d * LC_LD + i0);
+                const float4 k4 = *reinterpret_cast<const float4*>(Kt + d * LC_LD + j0);
+                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+            float4 out;
+            float* po = reinterpret_cast<float*>(&out);
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int i = i0 + a, j = j0 + b;
+                po[b] = j <= i ? acc[a][b] * pw[i - j] : 0.f;
+            }
+            *reinterpret_cast<float4*>(Ps + (i0 + a) * LC_LD + j0) = out;
+        }
+    }
+    __syncthreads();
+    if (r0 >= n) return;
+    float ap[2][4], as[2][4];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) { ap[a][b] = 0.f; as[a][b] = 0.f; }
+    const int jn = min(n, r0 + 2);
+#pragma unroll 4
+    for (int j = 0; j < jn; j++) {
+        const float p0 = Ps[r0 * LC_LD + j], p1 = Ps[(r0 + 1) * LC_LD + j];
+        const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * LC_COLS + c0);
+        ap[0][0] = fmaf(p0, v4.x, ap[0][0]); ap[0][1] = fmaf(p0, v4.y, ap[0][1]);
+        ap[0][2] = fmaf(p0, v4.z, ap[0][2]); ap[0][3] = fmaf(p0, v4.w, ap[0][3]);
+        ap[1][0] = fmaf(p1, v4.x, ap[1][0]); ap[1][1] = fmaf(p1, v4.y, ap[1][1]);
+        ap[1][2] = fmaf(p1, v4.z, ap[1][2]); ap[1][3] = fmaf(p1, v4.w, ap[1][3]);
+    }
+#pragma unroll 4
+    for (int d = 0; d < dim; d++) {
+        const float2 q2 = *reinterpret_cast<const float2*>(Qt + d * LC_LD + r0);
+        const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * LC_COLS + c0);
+        as[0][0] = fmaf(q2.x, s4.x, as[0][0]); as[0][1] = fmaf(q2.x, s4.y, as[0][1]);
+        as[0][2] = fmaf(q2.x, s4.z, as[0][2]); as[0][3] = fmaf(q2.x, s4.w, as[0][3]);
+        as[1][0] = fmaf(q2.y, s4.x, as[1][0]); as[1][1] = fmaf(q2.y, s4.y, as[1][1]);
+        as[1][2] = fmaf(q2.y, s4.z, as[1][2]); as[1][3] = fmaf(q2.y, s4.w, as[1][3]);
+    }
+#pragma unroll
+    for (int a = 0; a < 2; a++) {
+        const int i = r0 + a;
+        if (i >= n) continue;
+        const float w = pw[i + 1];
+        float* dst = o + (size_t)(t0 + i) * ldo + head * vdim + tile * LC_COLS + c0;
+#pragma unroll
+        for (int b = 0; b < 4; b++)
+            if (tile * LC_COLS + c0 + b < vdim) dst[b] = fmaf(w, as[a][b], ap[a][b]);
+    }
+}
+
 extern "C" {
 
 // qkv: rows [n, ld] in the storage type; q, k at columns q_col, k_col (H heads of dim), v at v_col (H heads of vdim).
@@ -388,6 +598,44 @@ int kp_lightning_chunked(const void* qkv, int ld, int q_col, int k_col, int v_co
         KP_DISPATCH_DTYPE(dtype, T, { if (act == 0) LC_LAUNCH(T, 0, false); else LC_LAUNCH(T, 1, false); });
     }
 #undef LC_LAUNCH
+    return kp_launch_status();
+}
+
+// The chunked form with the chunks in parallel.  chunk_seg, chunk_row0 [n_chunks]: every chunk's segment and first row
+// (chunks of at most kp_lightning_chunk_rows() rows, a segment's chunks in order and side by side); seg_chunk0 [n_seg + 1]:
+// the first chunk of every segment; scratch: n_chunks * H * dim * vdim floats.
+int kp_lightning_chunks(const void* qkv, int ld, int q_col, int k_col, int v_col, const float* decay_pow, float* state,
+                        const int* cu_rows, const int* seg_pos, const int* seg_slot, const int* chunk_seg, const int* chunk_row0,
+                        const int* seg_chunk0, int n_chunks, float* scratch, float* o, int ldo, int n_seg, int H, int dim, int vdim,
+                        int act, int write_state, int dtype, void* stream) {
+    if (n_seg <= 0 || n_chunks <= 0) return 0;
+    if (H < 1 || dim < 1 || vdim < 1 || act < 0 || act > 1) return KP_ERR_BAD_ARG;
+    const int tiles = (vdim + LC_COLS - 1) / LC_COLS;
+    if (dim > LC_MAX_DIM || H > 65535 || tiles > 65535 || (dim * vdim + 255) / 256 > 65535) return KP_ERR_UNSUPPORTED;
+    const size_t sm1 = ((size_t)dim * LC_LD + LC_C * LC_COLS + LC_C) * sizeof(float);
+    const size_t sm3 = ((size_t)2 * dim * LC_LD + LC_C * LC_COLS + LC_C * LC_LD + (size_t)dim * LC_COLS + LC_C + 4) * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+#define LC3_LAUNCH(T, ACT, VEC)                                                                                              \
+    do {                                                                                                                     \
+        if ((e = cudaFuncSetAttribute(lightning_chunk_sums_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm1)) != cudaSuccess) return (int)e; \
+        if ((e = cudaFuncSetAttribute(lightning_chunk_out_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm3)) != cudaSuccess) return (int)e; \
+        kp_launch_pdl(lightning_chunk_sums_kernel<T, ACT, VEC>, dim3(n_chunks, H, tiles), dim3(LC_THREADS), sm1, s, (const T*)qkv, ld, \
+                      k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, scratch, H, dim, vdim);                       \
+        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;                                                          \
+        kp_launch_pdl(lightning_chunk_states_kernel, dim3(n_seg, H, (dim * vdim + 255) / 256), dim3(256), 0, s, scratch, decay_pow, \
+                      state, cu_rows, seg_pos, seg_slot, seg_chunk0, chunk_row0, H, dim, vdim, write_state);                 \
+        if ((e = cudaGetLastError()) != cudaSuccess) return (int)e;                                                          \
+        kp_launch_pdl(lightning_chunk_out_kernel<T, ACT, VEC>, dim3(n_chunks, H, tiles), dim3(LC_THREADS), sm3, s, (const T*)qkv, ld, \
+                      q_col, k_col, v_col, decay_pow, cu_rows, chunk_seg, chunk_row0, (const float*)scratch, o, ldo, H, dim, vdim); \
+    } while (0)
+    const bool vec = dtype == KP_DTYPE_BF16 && dim % 8 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && !((uintptr_t)qkv & 15);
+    if (vec) {
+        if (act == 0) LC3_LAUNCH(bf16, 0, true); else LC3_LAUNCH(bf16, 1, true);
+    } else {
+        KP_DISPATCH_DTYPE(dtype, T, { if (act == 0) LC3_LAUNCH(T, 0, false); else LC3_LAUNCH(T, 1, false); });
+    }
+#undef LC3_LAUNCH
     return kp_launch_status();
 }
 

@@ -592,6 +592,39 @@ def lightning_chunked(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, dec
     return out
 
 
+def lightning_chunks(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_pow: torch.Tensor, state: torch.Tensor,
+                     cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor, chunk_seg: torch.Tensor,
+                     chunk_row0: torch.Tensor, seg_chunk0: torch.Tensor, n_chunks: int, out: torch.Tensor, n_seg: int,
+                     H: int, dim: int, vdim: int, activation: Optional[str] = "silu", write_state: bool = True) -> torch.Tensor:
+    """:func:`lightning_chunked` with the chunks of all segments computed side by side: every chunk's own sum, a
+    short serial pass over a segment's chunks for the states at their heads, every chunk's outputs.  ``chunk_seg`` /
+    ``chunk_row0`` [n_chunks]: a chunk's segment and first row (chunks of at most :func:`lightning_chunk_rows` rows,
+    a segment's chunks in order); ``seg_chunk0`` [n_seg + 1]: the first chunk of every segment."""
+    _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)
+    _need(decay_pow, "decay_pow", torch.float32)
+    for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot"), (chunk_seg, "chunk_seg"),
+                  (chunk_row0, "chunk_row0"), (seg_chunk0, "seg_chunk0")):
+        _need(t, nm, torch.int32)
+    n = qkv.shape[0]
+    if (tuple(out.shape) != (n, H * vdim) or tuple(state.shape[1:]) != (H, dim, vdim)
+            or tuple(decay_pow.shape) != (H, lightning_chunk_rows() + 1) or chunk_seg.numel() < n_chunks
+            or chunk_row0.numel() < n_chunks or seg_chunk0.numel() < n_seg + 1
+            or max(q_col, k_col) + H * dim > qkv.shape[1] or v_col + H * vdim > qkv.shape[1]):
+        raise KernelError("lightning_chunks: shape mismatch")
+    if activation not in ("silu", None):
+        raise KernelError("lightning_chunks: activation is silu or none")
+    if dim > LIGHTNING_CHUNK_MAX_DIM:
+        raise KernelError(f"lightning_chunks: dim={dim} exceeds {LIGHTNING_CHUNK_MAX_DIM}")
+    scratch = torch.empty(n_chunks * H * dim * vdim, dtype=torch.float32, device=qkv.device)
+    _run("lightning_chunks", load_library("lightning").kp_lightning_chunks, _ptr(qkv), _rows_2d(qkv, "qkv"), int(q_col),
+         int(k_col), int(v_col), _ptr(decay_pow), _ptr(state), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(chunk_seg),
+         _ptr(chunk_row0), _ptr(seg_chunk0), int(n_chunks), _ptr(scratch), _ptr(out), _rows_2d(out, "out"), int(n_seg), H, dim,
+         vdim, 0 if activation == "silu" else 1, int(bool(write_state)), dtype_code(qkv.dtype), STREAM,
+         work=(4 * n * H * dim * vdim, 0))
+    LAUNCHES[0] += 2
+    return out
+
+
 # ------------------------------------------------------------------ attention
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], eps: float,

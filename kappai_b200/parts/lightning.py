@@ -15,8 +15,11 @@ product; the recurrence, the norm and the gate are float32 (csrc/lightning.cu,
 ``norm_gate_rows``).  Decoded tokens and short portions run the scan kernel
 (row after row, the same bits however a sequence is cut; the 32-bit mode runs
 it always); in 16-bit mode a step with a portion of ``CHUNKED_FROM`` rows or
-more runs the chunked kernel (the rows of a chunk as small float32 matrix
-products).
+more runs the chunked kernels (the rows of a chunk as small float32 matrix
+products): with few segments the chunks of all segments side by side (the
+list of chunks is a step table built on the host), with enough segments and
+heads to fill the device a block a (segment, head, 32 value columns) that
+walks its chunks itself.
 
 Params: hidden_size, num_heads, head_dim, value_dim, decay (a list, one a
 head), norm_eps, activation ("silu" | None), gate ("sigmoid").
@@ -35,7 +38,27 @@ from ..ops.linear import linear
 from .base import Part, WeightSpec, register_part
 
 
-CHUNKED_FROM = 16      # rows of a step's longest segment from which the chunked kernel runs (16-bit mode)
+CHUNKED_FROM = 16      # rows of a step's longest segment from which the chunked kernels run (16-bit mode)
+
+
+def lightning_chunks(segs, chunk_rows: int):
+    """The chunks of a step's segments for the chunked kernels (``engine.batch.StepSegments`` in,
+    ``engine.batch.PartTables`` out; None for a step of short segments only, which the scan takes): every segment cut
+    into stretches of at most ``chunk_rows`` rows, counted from its first row in this step."""
+    from ..engine.batch import PartTables
+
+    if segs.max_seg_len < CHUNKED_FROM:
+        return None
+    cu = segs.cu_rows
+    chunk_seg, chunk_row0, seg_chunk0 = [], [], [0]
+    for i in range(segs.n_seg):
+        for r0 in range(int(cu[i]), int(cu[i + 1]), chunk_rows):
+            chunk_seg.append(i)
+            chunk_row0.append(r0)
+        seg_chunk0.append(len(chunk_seg))
+    i32 = lambda v: np.asarray(v, dtype=np.int32)
+    return PartTables(arrays={"chunk_seg": i32(chunk_seg), "chunk_row0": i32(chunk_row0), "seg_chunk0": i32(seg_chunk0)},
+                      scalars={"n_chunks": len(chunk_seg)})
 
 
 class LightningAttention(Part):
@@ -62,6 +85,13 @@ class LightningAttention(Part):
             raise ConfigError("lightning: the output gate is a sigmoid")
         if min(self.H, self.dim, self.vdim) < 1 or self.dim > K.LIGHTNING_MAX_DIM:
             raise ConfigError(f"lightning: head_dim={self.dim} is not supported by the kernels (1 to {K.LIGHTNING_MAX_DIM})")
+        self.chunked = env.dtype != torch.float32 and self.dim <= K.LIGHTNING_CHUNK_MAX_DIM and env.device.type == "cuda"
+        if self.chunked:
+            self.chunk_rows = K.lightning_chunk_rows()
+            self.step_tables_key = ("lightning_chunks", self.chunk_rows)
+
+    def step_tables(self, segs):
+        return lightning_chunks(segs, self.chunk_rows)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         d, H = self.d, self.H
@@ -82,8 +112,9 @@ class LightningAttention(Part):
         self.decay_lo = torch.from_numpy(lo).to(dev)
         # the chunked kernel's table of powers a^0 .. a^rows, made in double
         self.decay_pow = None
-        if dev.type == "cuda" and self.env.dtype != torch.float32 and self.dim <= K.LIGHTNING_CHUNK_MAX_DIM:
-            m = np.arange(K.lightning_chunk_rows() + 1, dtype=np.float64)
+        if self.chunked:
+            self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+            m = np.arange(self.chunk_rows + 1, dtype=np.float64)
             self.decay_pow = torch.from_numpy(np.power(a[:, None], m[None, :]).astype(np.float32)).contiguous().to(dev)
 
     def cache_spec(self):
@@ -94,9 +125,17 @@ class LightningAttention(Part):
         H, dim, vdim, n = self.H, self.dim, self.vdim, ctx.n_rows
         p = linear(h, self.w_in)                                 # [q | k | v | gate]
         o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
-        if self.decay_pow is not None and ctx.max_seg_len >= CHUNKED_FROM:
+        chunks = ctx.tables.get(self.step_tables_key) if self.chunked else None
+        if chunks is not None and 2 * ctx.n_seg * H * -(-vdim // 32) > self.n_sm:
+            # enough (segment, head, 32 value columns) blocks to fill the device: a block walks its segment's chunks itself
             K.lightning_chunked(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos,
                                 ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
+        elif chunks is not None:
+            # few segments: all their chunks side by side (measured at 2,048 rows: 32 heads of 64 x 64 176 us against
+            # 393; 32 heads of 128 x 128 and four segments of 32 heads of 64 x 64 are 8 and 35 % slower this way)
+            K.lightning_chunks(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos, ctx.seg_slot,
+                               chunks.chunk_seg, chunks.chunk_row0, chunks.seg_chunk0, chunks.n_chunks, o, ctx.n_seg, H, dim,
+                               vdim, self.activation, cache.writes)
         else:
             K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows, ctx.seg_pos,
                              ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
