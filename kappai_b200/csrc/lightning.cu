@@ -8,21 +8,19 @@
 // thousand steps of it do not drift from the constant the model gives), the products and the sums.  The state of a
 // request lives in its slot between steps and counts as zero at position 0.
 //
-// Three forms.  The scan: a block walks the rows of one (segment, head, 16 value columns) in order, the state in
+// Two forms.  The scan: a block walks the rows of one (segment, head, 16 value columns) in order, the state in
 // registers (thread = (value column, a sixteenth of the key rows)); rows are staged 16 (or 8) at a time, q and k with
 // their activation applied once, and a thread reads its stretch of them as float4.  One row a segment is the decode
 // step.  Every sum has a fixed order that depends on the head's size alone, so a row's bits do not depend on how the
 // sequence was cut or on what else is in the batch.
 //
-// The chunked form, for prompt portions in 16-bit mode: a block takes one (segment, head, 32 value columns) and
-// walks the segment in chunks of LC_C rows; within a chunk the rows are independent given the state S at its head,
+// The chunked form, for prompt portions in 16-bit mode: a segment in chunks of LC_C rows; within a chunk the rows are
+// independent given the state S at its head,
 //   o_i = sum_{j <= i} a^(i-j) (q_i . k_j) v_j + a^(i+1) q_i^T S ,     S' = a^n S + sum_j a^(n-1-j) k_j v_j^T ,
 // three small float32 matrix products from shared memory (q and k staged transposed, so that every product reads
-// its operands along rows) instead of LC_C dependent steps.  The powers of the decay come from a table made in
-// double on the host.  Sums have another order than the scan's, so the 32-bit mode keeps the scan.
-//
-// The chunks in parallel, for steps of few segments (one long prompt): the same products with the chunks of all
-// segments side by side and a short serial pass between them (see "chunks in parallel" below).
+// its operands along rows) instead of LC_C dependent steps.  The chunks of all segments run side by side with a
+// short serial pass between them (see "chunks in parallel" below).  The powers of the decay come from a table made
+// in double on the host.  Sums have another order than the scan's, so the 32-bit mode keeps the scan.
 #include "common.cuh"
 
 #define LT_CH_MAX 16             // rows staged at a time by the scan (half as many for the largest heads: shared memory)
@@ -134,212 +132,11 @@ lightning_scan_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, i
 #define LC_THREADS 256
 #define LC_MAX_DIM 128
 
-#define LC_PRE (LC_MAX_DIM / 8 * LC_C / LC_THREADS)        // 16-byte loads a thread has in flight for q (and for k)
-
-// The q and k columns of the chunk at row t0, 16 bytes a load, into registers (rows behind row1 are not read).
-template <typename T>
-__device__ __forceinline__ void lc_fetch(uint4* pre_q, uint4* pre_k, const T* __restrict__ qkv, int ld, int q_col, int k_col,
-                                         int head, int dim, int t0, int row1, int tid) {
-    const int ng = dim / 8;
-#pragma unroll
-    for (int u = 0; u < LC_PRE; u++) {
-        const int x = tid + u * LC_THREADS;
-        const int t = x % LC_C, g = x / LC_C;
-        if (x < ng * LC_C && t0 + t < row1) {
-            const T* row = qkv + (size_t)(t0 + t) * ld + head * dim + g * 8;
-            pre_q[u] = __ldg(reinterpret_cast<const uint4*>(row + q_col));
-            pre_k[u] = __ldg(reinterpret_cast<const uint4*>(row + k_col));
-        }
-    }
-}
-
-// VEC: 16-bit rows whose q and k columns are 16-byte aligned (dim a multiple of 8): fetched 16 bytes a load, a chunk ahead.
-template <typename T, int ACT, bool VEC>
-__global__ void __launch_bounds__(LC_THREADS)
-lightning_chunked_kernel(const T* __restrict__ qkv, int ld, int q_col, int k_col, int v_col, const float* __restrict__ decay_pow,
-                         float* __restrict__ state, const int* __restrict__ cu_rows, const int* __restrict__ seg_pos,
-                         const int* __restrict__ seg_slot, float* __restrict__ o, int ldo, int H, int dim, int vdim,
-                         int write_state) {
-    kp_pdl_begin();
-    extern __shared__ __align__(16) float lc_sm[];
-    float* Qt = lc_sm;                                           // [dim][LC_LD]: q of the chunk, transposed
-    float* Kt = Qt + (size_t)dim * LC_LD;                        // [dim][LC_LD]
-    float* Vs = Kt + (size_t)dim * LC_LD;                        // [LC_C][LC_COLS]
-    float* Ps = Vs + LC_C * LC_COLS;                             // [LC_C][LC_LD]: decayed, masked q k^T
-    float* Ss = Ps + LC_C * LC_LD;                               // [dim][LC_COLS]: the state
-    float* pw = Ss + (size_t)dim * LC_COLS;                      // [LC_C + 1]: a^m
-    float* kw = pw + LC_C + 4;                                   // [LC_C]: a^(n-1-j), 0 behind the chunk's rows
-    const int seg = blockIdx.x, head = blockIdx.y, tile = blockIdx.z;
-    const int tid = threadIdx.x;
-    float* st = state + (((size_t)seg_slot[seg] * H + head) * dim) * vdim;
-    const bool fresh = seg_pos[seg] == 0;
-    for (int x = tid; x < dim * LC_COLS; x += LC_THREADS) {
-        const int d = x / LC_COLS, c = x % LC_COLS, j = tile * LC_COLS + c;
-        Ss[x] = (!fresh && j < vdim) ? st[(size_t)d * vdim + j] : 0.f;
-    }
-    for (int x = tid; x <= LC_C; x += LC_THREADS) pw[x] = decay_pow[(size_t)head * (LC_C + 1) + x];
-    const int row0 = cu_rows[seg], row1 = cu_rows[seg + 1];
-    uint4 pre_q[LC_PRE], pre_k[LC_PRE];
-    if (VEC) lc_fetch<T>(pre_q, pre_k, qkv, ld, q_col, k_col, head, dim, row0, row1, tid);
-    // products 1 (P): rows i0 .. i0 + 3, columns j0 .. j0 + 3; products 2 and 3: two rows, four value columns
-    const int i0 = (tid / 16) * 4, j0 = (tid % 16) * 4;
-    const int r0 = (tid / 8) * 2, c0 = (tid % 8) * 4;
-    for (int t0 = row0; t0 < row1; t0 += LC_C) {
-        const int n = min(LC_C, row1 - t0);
-        __syncthreads();                                         // the chunk before is done with the tiles
-        if (VEC) {
-            // the rows fetched ahead (16 bytes = 8 columns a load) go to the tiles; then the next chunk's are fetched
-            const int ng = dim / 8;
-#pragma unroll
-            for (int u = 0; u < LC_PRE; u++) {
-                const int x = tid + u * LC_THREADS;
-                if (x < ng * LC_C) {
-                    const int t = x % LC_C, g = x / LC_C;
-                    const bf16* qe = reinterpret_cast<const bf16*>(&pre_q[u]);
-                    const bf16* ke = reinterpret_cast<const bf16*>(&pre_k[u]);
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        Qt[(g * 8 + e) * LC_LD + t] = t < n ? lt_act<ACT>(__bfloat162float(qe[e])) : 0.f;
-                        Kt[(g * 8 + e) * LC_LD + t] = t < n ? lt_act<ACT>(__bfloat162float(ke[e])) : 0.f;
-                    }
-                }
-            }
-            lc_fetch<T>(pre_q, pre_k, qkv, ld, q_col, k_col, head, dim, t0 + LC_C, row1, tid);
-        } else {
-            for (int x = tid; x < dim * LC_C; x += LC_THREADS) {
-                const int t = x % LC_C, d = x / LC_C;
-                float qv = 0.f, kv = 0.f;
-                if (t < n) {
-                    const T* row = qkv + (size_t)(t0 + t) * ld + head * dim + d;
-                    qv = lt_act<ACT>(to_f32(row[q_col]));
-                    kv = lt_act<ACT>(to_f32(row[k_col]));
-                }
-                Qt[d * LC_LD + t] = qv;
-                Kt[d * LC_LD + t] = kv;
-            }
-        }
-        for (int x = tid; x < LC_C * LC_COLS; x += LC_THREADS) {
-            const int t = x / LC_COLS, c = x % LC_COLS, j = tile * LC_COLS + c;
-            Vs[x] = (t < n && j < vdim) ? lt_act<ACT>(to_f32(qkv[(size_t)(t0 + t) * ld + v_col + head * vdim + j])) : 0.f;
-        }
-        for (int x = tid; x < LC_C; x += LC_THREADS) kw[x] = x < n ? pw[n - 1 - x] : 0.f;
-        __syncthreads();
-        // 1. P[i][j] = a^(i-j) (q_i . k_j) for j <= i
-        {
-            float acc[4][4];
-#pragma unroll
-            for (int a = 0; a < 4; a++)
-#pragma unroll
-                for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
-            if (j0 <= i0 + 3) {                                  // (a tile above the diagonal is all masked)
-#pragma unroll 4
-                for (int d = 0; d < dim; d++) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(Qt + d * LC_LD + i0);
-                    const float4 k4 = *reinterpret_cast<const float4*>(Kt + d * LC_LD + j0);
-                    const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-                    for (int a = 0; a < 4; a++)
-#pragma unroll
-                        for (int b = 0; b < 4; b++) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
-                }
-            }
-#pragma unroll
-            for (int a = 0; a < 4; a++) {
-                float4 out;
-                float* po = reinterpret_cast<float*>(&out);
-#pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    const int i = i0 + a, j = j0 + b;
-                    po[b] = j <= i ? acc[a][b] * pw[i - j] : 0.f;
-                }
-                *reinterpret_cast<float4*>(Ps + (i0 + a) * LC_LD + j0) = out;
-            }
-        }
-        __syncthreads();
-        // 2. o_i = sum_j P[i][j] v_j + a^(i+1) q_i^T S
-        {
-            float ap[2][4], as[2][4];
-#pragma unroll
-            for (int a = 0; a < 2; a++)
-#pragma unroll
-                for (int b = 0; b < 4; b++) { ap[a][b] = 0.f; as[a][b] = 0.f; }
-            const int jn = min(n, r0 + 2);                       // (P is zero behind the diagonal and behind the chunk's rows)
-#pragma unroll 4
-            for (int j = 0; j < jn; j++) {
-                const float p0 = Ps[r0 * LC_LD + j], p1 = Ps[(r0 + 1) * LC_LD + j];
-                const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * LC_COLS + c0);
-                ap[0][0] = fmaf(p0, v4.x, ap[0][0]); ap[0][1] = fmaf(p0, v4.y, ap[0][1]);
-                ap[0][2] = fmaf(p0, v4.z, ap[0][2]); ap[0][3] = fmaf(p0, v4.w, ap[0][3]);
-                ap[1][0] = fmaf(p1, v4.x, ap[1][0]); ap[1][1] = fmaf(p1, v4.y, ap[1][1]);
-                ap[1][2] = fmaf(p1, v4.z, ap[1][2]); ap[1][3] = fmaf(p1, v4.w, ap[1][3]);
-            }
-#pragma unroll 4
-            for (int d = 0; d < dim; d++) {
-                const float2 q2 = *reinterpret_cast<const float2*>(Qt + d * LC_LD + r0);
-                const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * LC_COLS + c0);
-                as[0][0] = fmaf(q2.x, s4.x, as[0][0]); as[0][1] = fmaf(q2.x, s4.y, as[0][1]);
-                as[0][2] = fmaf(q2.x, s4.z, as[0][2]); as[0][3] = fmaf(q2.x, s4.w, as[0][3]);
-                as[1][0] = fmaf(q2.y, s4.x, as[1][0]); as[1][1] = fmaf(q2.y, s4.y, as[1][1]);
-                as[1][2] = fmaf(q2.y, s4.z, as[1][2]); as[1][3] = fmaf(q2.y, s4.w, as[1][3]);
-            }
-#pragma unroll
-            for (int a = 0; a < 2; a++) {
-                const int i = r0 + a;
-                if (i >= n) continue;
-                const float w = pw[i + 1];
-                float* dst = o + (size_t)(t0 + i) * ldo + head * vdim + tile * LC_COLS + c0;
-#pragma unroll
-                for (int b = 0; b < 4; b++)
-                    if (tile * LC_COLS + c0 + b < vdim) dst[b] = fmaf(w, as[a][b], ap[a][b]);
-            }
-        }
-        __syncthreads();                                         // everyone has read the state at the chunk's head
-        // 3. S <- a^n S + sum_j a^(n-1-j) k_j v_j^T
-        {
-            const float wn = pw[n];
-            for (int d0 = r0; d0 < dim; d0 += 2 * (LC_THREADS / 8)) {
-                float acc[2][4];
-#pragma unroll
-                for (int a = 0; a < 2; a++)
-#pragma unroll
-                    for (int b = 0; b < 4; b++) acc[a][b] = 0.f;
-                const bool two = d0 + 1 < dim;
-#pragma unroll 4
-                for (int j = 0; j < n; j++) {
-                    const float w = kw[j];
-                    const float k0 = Kt[d0 * LC_LD + j] * w, k1 = two ? Kt[(d0 + 1) * LC_LD + j] * w : 0.f;
-                    const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * LC_COLS + c0);
-                    acc[0][0] = fmaf(k0, v4.x, acc[0][0]); acc[0][1] = fmaf(k0, v4.y, acc[0][1]);
-                    acc[0][2] = fmaf(k0, v4.z, acc[0][2]); acc[0][3] = fmaf(k0, v4.w, acc[0][3]);
-                    acc[1][0] = fmaf(k1, v4.x, acc[1][0]); acc[1][1] = fmaf(k1, v4.y, acc[1][1]);
-                    acc[1][2] = fmaf(k1, v4.z, acc[1][2]); acc[1][3] = fmaf(k1, v4.w, acc[1][3]);
-                }
-#pragma unroll
-                for (int a = 0; a < 2; a++) {
-                    if (d0 + a >= dim) continue;
-                    float* sp = Ss + (d0 + a) * LC_COLS + c0;
-#pragma unroll
-                    for (int b = 0; b < 4; b++) sp[b] = fmaf(wn, sp[b], acc[a][b]);
-                }
-            }
-        }
-    }
-    __syncthreads();
-    if (write_state) {
-        for (int x = tid; x < dim * LC_COLS; x += LC_THREADS) {
-            const int d = x / LC_COLS, c = x % LC_COLS, j = tile * LC_COLS + c;
-            if (j < vdim) st[(size_t)d * vdim + j] = Ss[x];
-        }
-    }
-}
-
-
 // ------------------------------------------------------------------------------------------ chunks in parallel
-// The chunked form with the chunks of all segments side by side (a list built on the host: chunk -> segment, first
-// row): (1) every chunk's own sum U_c = sum_j a^(n-1-j) k_j v_j^T, all chunks at once; (2) a short serial pass a
+// The chunks of all segments side by side (a list built on the host: chunk -> segment, first row): (1) every chunk's own sum U_c = sum_j a^(n-1-j) k_j v_j^T, all chunks at once; (2) a short serial pass a
 // (segment, head) turns the sums into the states at the chunks' heads, S_(c+1) = a^n S_c + U_c, in place, and leaves
 // the segment's last state in its slot; (3) every chunk's outputs from its state and its own rows, all chunks at once.
-// The products are those of the kernel above; only (2) is serial, and it is one multiply-add an element and chunk.
+// Only (2) is serial, and it is one multiply-add an element and chunk.
 
 // A [rows t0 .. t0 + n) x [dim] stretch of columns, with the activation, transposed into dst [dim][LC_LD]
 // (zeros behind the n rows).
@@ -434,12 +231,27 @@ lightning_chunk_states_kernel(float* __restrict__ U, const float* __restrict__ d
     float* st = state + (((size_t)seg_slot[seg] * H + head) * dim) * vdim + e;
     float S = seg_pos[seg] == 0 ? 0.f : *st;
     const int row1 = cu_rows[seg + 1];
-    for (int c = seg_chunk0[seg]; c < seg_chunk0[seg + 1]; c++) {
-        const int n = min(LC_C, row1 - chunk_row0[c]);
-        float* p = U + ((size_t)c * H + head) * dim * vdim + e;
-        const float u = *p;
-        *p = S;
-        S = fmaf(decay_pow[(size_t)head * (LC_C + 1) + n], S, u);
+    // (eight chunks' sums are fetched at once: the serial part is then the multiply-adds alone, not the loads' latency)
+    const size_t stride = (size_t)H * dim * vdim;
+    const int c_end = seg_chunk0[seg + 1];
+    for (int c0 = seg_chunk0[seg]; c0 < c_end; c0 += 8) {
+        float* p = U + ((size_t)c0 * H + head) * dim * vdim + e;
+        float u[8];
+        float w[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            if (c0 + k < c_end) {
+                u[k] = p[k * stride];
+                w[k] = decay_pow[(size_t)head * (LC_C + 1) + min(LC_C, row1 - chunk_row0[c0 + k])];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            if (c0 + k < c_end) {
+                p[k * stride] = S;
+                S = fmaf(w[k], S, u[k]);
+            }
+        }
     }
     if (write_state) *st = S;
 }
@@ -573,35 +385,8 @@ int kp_lightning_scan(const void* qkv, int ld, int q_col, int k_col, int v_col, 
 // Rows of a chunk of the chunked form (the decay table holds a^0 .. a^rows for every head).
 int kp_lightning_chunk_rows() { return LC_C; }
 
-// The same contract as kp_lightning_scan with the decays given as powers: decay_pow [H][rows + 1], a_h^m.
-// KP_ERR_UNSUPPORTED for heads it does not take (dim > 128).
-int kp_lightning_chunked(const void* qkv, int ld, int q_col, int k_col, int v_col, const float* decay_pow, float* state,
-                         const int* cu_rows, const int* seg_pos, const int* seg_slot, float* o, int ldo, int n_seg, int H,
-                         int dim, int vdim, int act, int write_state, int dtype, void* stream) {
-    if (n_seg <= 0) return 0;
-    if (H < 1 || dim < 1 || vdim < 1 || act < 0 || act > 1) return KP_ERR_BAD_ARG;
-    if (dim > LC_MAX_DIM || H > 65535 || (vdim + LC_COLS - 1) / LC_COLS > 65535) return KP_ERR_UNSUPPORTED;
-    const dim3 grid(n_seg, H, (vdim + LC_COLS - 1) / LC_COLS), block(LC_THREADS);
-    const size_t sm = ((size_t)2 * dim * LC_LD + LC_C * LC_COLS + LC_C * LC_LD + (size_t)dim * LC_COLS + 2 * (LC_C + 4)) * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
-#define LC_LAUNCH(T, ACT, VEC)                                                                                               \
-    do {                                                                                                                     \
-        cudaError_t e = cudaFuncSetAttribute(lightning_chunked_kernel<T, ACT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-        if (e != cudaSuccess) return (int)e;                                                                                 \
-        kp_launch_pdl(lightning_chunked_kernel<T, ACT, VEC>, grid, block, sm, s, (const T*)qkv, ld, q_col, k_col, v_col, decay_pow, state, \
-                      cu_rows, seg_pos, seg_slot, o, ldo, H, dim, vdim, write_state);                                        \
-    } while (0)
-    const bool vec = dtype == KP_DTYPE_BF16 && dim % 8 == 0 && ld % 8 == 0 && q_col % 8 == 0 && k_col % 8 == 0 && !((uintptr_t)qkv & 15);
-    if (vec) {
-        if (act == 0) LC_LAUNCH(bf16, 0, true); else LC_LAUNCH(bf16, 1, true);
-    } else {
-        KP_DISPATCH_DTYPE(dtype, T, { if (act == 0) LC_LAUNCH(T, 0, false); else LC_LAUNCH(T, 1, false); });
-    }
-#undef LC_LAUNCH
-    return kp_launch_status();
-}
-
-// The chunked form with the chunks in parallel.  chunk_seg, chunk_row0 [n_chunks]: every chunk's segment and first row
+// The chunked form: the contract of kp_lightning_scan with the decays given as powers, decay_pow [H][rows + 1] = a_h^m,
+// and the list of chunks.  KP_ERR_UNSUPPORTED for heads it does not take (dim > 128).  chunk_seg, chunk_row0 [n_chunks]: every chunk's segment and first row
 // (chunks of at most kp_lightning_chunk_rows() rows, a segment's chunks in order and side by side); seg_chunk0 [n_seg + 1]:
 // the first chunk of every segment; scratch: n_chunks * H * dim * vdim floats.
 int kp_lightning_chunks(const void* qkv, int ld, int q_col, int k_col, int v_col, const float* decay_pow, float* state,

@@ -562,42 +562,18 @@ LIGHTNING_CHUNK_MAX_DIM = 128    # key rows of a head that the chunked form hold
 
 
 def lightning_chunk_rows() -> int:
-    """Rows of a chunk of :func:`lightning_chunked` (its decay table holds the powers 0 .. rows of every head's decay)."""
+    """Rows of a chunk of :func:`lightning_chunks` (its decay table holds the powers 0 .. rows of every head's decay)."""
     return int(load_library("lightning").kp_lightning_chunk_rows())
-
-
-def lightning_chunked(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_pow: torch.Tensor, state: torch.Tensor,
-                      cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor, out: torch.Tensor, n_seg: int,
-                      H: int, dim: int, vdim: int, activation: Optional[str] = "silu", write_state: bool = True) -> torch.Tensor:
-    """The recurrence of :func:`lightning_scan` for segments of many rows: chunks of rows as small matrix products
-    (float32 on the CUDA cores), the state carried from chunk to chunk.  ``decay_pow``: float32 [H, rows + 1], the
-    powers ``a_h^m`` (made in double).  Sums have another order than the scan's."""
-    _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)
-    _need(decay_pow, "decay_pow", torch.float32)
-    for t, nm in ((cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
-        _need(t, nm, torch.int32)
-    n = qkv.shape[0]
-    if (tuple(out.shape) != (n, H * vdim) or tuple(state.shape[1:]) != (H, dim, vdim)
-            or tuple(decay_pow.shape) != (H, lightning_chunk_rows() + 1)
-            or max(q_col, k_col) + H * dim > qkv.shape[1] or v_col + H * vdim > qkv.shape[1]):
-        raise KernelError("lightning_chunked: shape mismatch")
-    if activation not in ("silu", None):
-        raise KernelError("lightning_chunked: activation is silu or none")
-    if dim > LIGHTNING_CHUNK_MAX_DIM:
-        raise KernelError(f"lightning_chunked: dim={dim} exceeds {LIGHTNING_CHUNK_MAX_DIM}")
-    _run("lightning_chunked", load_library("lightning").kp_lightning_chunked, _ptr(qkv), _rows_2d(qkv, "qkv"), int(q_col),
-         int(k_col), int(v_col), _ptr(decay_pow), _ptr(state), _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(out),
-         _rows_2d(out, "out"), int(n_seg), H, dim, vdim, 0 if activation == "silu" else 1, int(bool(write_state)),
-         dtype_code(qkv.dtype), STREAM, work=(4 * n * H * dim * vdim, 0))
-    return out
 
 
 def lightning_chunks(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay_pow: torch.Tensor, state: torch.Tensor,
                      cu_rows: torch.Tensor, seg_pos: torch.Tensor, seg_slot: torch.Tensor, chunk_seg: torch.Tensor,
                      chunk_row0: torch.Tensor, seg_chunk0: torch.Tensor, n_chunks: int, out: torch.Tensor, n_seg: int,
                      H: int, dim: int, vdim: int, activation: Optional[str] = "silu", write_state: bool = True) -> torch.Tensor:
-    """:func:`lightning_chunked` with the chunks of all segments computed side by side: every chunk's own sum, a
-    short serial pass over a segment's chunks for the states at their heads, every chunk's outputs.  ``chunk_seg`` /
+    """The recurrence of :func:`lightning_scan` for segments of many rows: chunks of rows as small matrix products
+    (float32 on the CUDA cores), the chunks of all segments side by side: every chunk's own sum, a short serial pass
+    over a segment's chunks for the states at their heads, every chunk's outputs.  ``decay_pow``: float32
+    [H, rows + 1], the powers ``a_h^m`` (made in double).  Sums have another order than the scan's.  ``chunk_seg`` /
     ``chunk_row0`` [n_chunks]: a chunk's segment and first row (chunks of at most :func:`lightning_chunk_rows` rows,
     a segment's chunks in order); ``seg_chunk0`` [n_seg + 1]: the first chunk of every segment."""
     _need(qkv, "qkv", contiguous=False); _need(out, "out", torch.float32); _need(state, "state", torch.float32)

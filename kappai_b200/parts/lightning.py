@@ -16,10 +16,8 @@ product; the recurrence, the norm and the gate are float32 (csrc/lightning.cu,
 (row after row, the same bits however a sequence is cut; the 32-bit mode runs
 it always); in 16-bit mode a step with a portion of ``CHUNKED_FROM`` rows or
 more runs the chunked kernels (the rows of a chunk as small float32 matrix
-products): with few segments the chunks of all segments side by side (the
-list of chunks is a step table built on the host), with enough segments and
-heads to fill the device a block a (segment, head, 32 value columns) that
-walks its chunks itself.
+products, the chunks of all segments side by side; the list of chunks is a
+step table built on the host).
 
 Params: hidden_size, num_heads, head_dim, value_dim, decay (a list, one a
 head), norm_eps, activation ("silu" | None), gate ("sigmoid").
@@ -113,7 +111,6 @@ class LightningAttention(Part):
         # the chunked kernel's table of powers a^0 .. a^rows, made in double
         self.decay_pow = None
         if self.chunked:
-            self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
             m = np.arange(self.chunk_rows + 1, dtype=np.float64)
             self.decay_pow = torch.from_numpy(np.power(a[:, None], m[None, :]).astype(np.float32)).contiguous().to(dev)
 
@@ -126,13 +123,8 @@ class LightningAttention(Part):
         p = linear(h, self.w_in)                                 # [q | k | v | gate]
         o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
         chunks = ctx.tables.get(self.step_tables_key) if self.chunked else None
-        if chunks is not None and 2 * ctx.n_seg * H * -(-vdim // 32) > self.n_sm:
-            # enough (segment, head, 32 value columns) blocks to fill the device: a block walks its segment's chunks itself
-            K.lightning_chunked(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos,
-                                ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
-        elif chunks is not None:
-            # few segments: all their chunks side by side (measured at 2,048 rows: 32 heads of 64 x 64 176 us against
-            # 393; 32 heads of 128 x 128 and four segments of 32 heads of 64 x 64 are 8 and 35 % slower this way)
+        if chunks is not None:
+            # (measured at 2,048 rows against the scan: 32 heads of 64 x 64 151 us against 430, of 128 x 128 620 against 1291)
             K.lightning_chunks(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos, ctx.seg_slot,
                                chunks.chunk_seg, chunks.chunk_row0, chunks.seg_chunk0, chunks.n_chunks, o, ctx.n_seg, H, dim,
                                vdim, self.activation, cache.writes)

@@ -71,8 +71,6 @@ def _chunk_lists(cu):
 @pytest.mark.parametrize("kernel,H,dim,vdim,decay", [
     ("scan", 2, 16, 32, [0.9, 0.995]), ("scan", 3, 40, 24, [0.3, 1.0, 0.999]), ("scan", 1, 128, 64, [0.97]),
     ("scan", 2, 256, 8, [0.5, 0.99]), ("scan", 1, 1, 1, [0.75]), ("scan", 4, 64, 64, [0.6, 0.9, 0.99, 0.9999]),
-    ("chunked", 2, 16, 32, [0.9, 0.995]), ("chunked", 3, 40, 24, [0.3, 1.0, 0.999]), ("chunked", 1, 128, 64, [0.97]),
-    ("chunked", 2, 30, 70, [0.5, 0.99]), ("chunked", 1, 1, 1, [0.75]), ("chunked", 4, 64, 64, [0.6, 0.9, 0.99, 0.9999]),
     ("chunks", 2, 16, 32, [0.9, 0.995]), ("chunks", 3, 40, 24, [0.3, 1.0, 0.999]), ("chunks", 1, 128, 64, [0.97]),
     ("chunks", 2, 30, 70, [0.5, 0.99]), ("chunks", 1, 1, 1, [0.75]), ("chunks", 4, 64, 64, [0.6, 0.9, 0.99, 0.9999])])
 def test_lightning_kernels_segments_states_and_slots(kernel, H, dim, vdim, decay, dtype):
@@ -81,7 +79,7 @@ def test_lightning_kernels_segments_states_and_slots(kernel, H, dim, vdim, decay
     state is zeroed by position 0 alone."""
     from kappai_b200.ops import kernels as K
     rng = np.random.default_rng(dim * 7 + vdim)
-    lens, cut = [37, 150, 1], [37, 18, 1]                                # (150 rows: three chunks of the chunked kernel)
+    lens, cut = [37, 150, 1], [37, 18, 1]                                # (150 rows: three chunks of the chunked kernels)
     width = 2 * H * dim + H * vdim + 5                                   # columns q | k | 5 others | v
     rows = {i: rt(rng.normal(0, 1, (L + 6, width)), dtype) for i, L in enumerate(lens)}
     slots = [2, 0, 3]
@@ -109,11 +107,8 @@ def test_lightning_kernels_segments_states_and_slots(kernel, H, dim, vdim, decay
             K.lightning_scan(dev(x, dtype), q_col, k_col, v_col, dhi, dlo, state, *seg, o, len(pieces), H, dim, vdim, "silu", True)
         else:
             pw = np.power(a[:, None], np.arange(K.lightning_chunk_rows() + 1)[None, :])
-            if kernel == "chunked":
-                K.lightning_chunked(dev(x, dtype), q_col, k_col, v_col, dev(pw), state, *seg, o, len(pieces), H, dim, vdim, "silu", True)
-            else:
-                K.lightning_chunks(dev(x, dtype), q_col, k_col, v_col, dev(pw), state, *seg, *_chunk_lists(cu), o, len(pieces), H,
-                                   dim, vdim, "silu", True)
+            K.lightning_chunks(dev(x, dtype), q_col, k_col, v_col, dev(pw), state, *seg, *_chunk_lists(cu), o, len(pieces), H, dim,
+                               vdim, "silu", True)
         o = o.cpu().double().numpy().reshape(-1, H, vdim)
         for (i, p, n), r0 in zip(pieces, cu[:-1]):
             got[i][p:p + n] = o[r0:r0 + n]
@@ -128,7 +123,7 @@ def test_lightning_kernels_segments_states_and_slots(kernel, H, dim, vdim, decay
         assert np.abs(got[i] - want[i]).max() <= tol * max(scale, 1.0), (i, np.abs(got[i] - want[i]).max(), scale)
 
 
-@pytest.mark.parametrize("kernel", ["scan", "chunked", "chunks"])
+@pytest.mark.parametrize("kernel", ["scan", "chunks"])
 def test_lightning_a_far_key_counts_and_the_decay_does_not_drift(kernel):
     """With a decay of 1 - 1e-4 over 3000 rows the first key's share is exp(-0.3); one key far back is made a hundred
     times larger than the rest, so that losing it, or a decay rounded to float32 alone, shows in the last rows."""
@@ -152,14 +147,11 @@ def test_lightning_a_far_key_counts_and_the_decay_does_not_drift(kernel):
                              vdim, None, True)
         else:
             pw = np.power(a[:, None], np.arange(K.lightning_chunk_rows() + 1)[None, :])
-            if kernel == "chunked":
-                K.lightning_chunked(dev(x[r0:r1]), 0, 8, 16, dev(pw), state, *seg, o[r0:r1], 1, H, dim, vdim, None, True)
-            else:
-                K.lightning_chunks(dev(x[r0:r1]), 0, 8, 16, dev(pw), state, *seg, *_chunk_lists([0, r1 - r0]), o[r0:r1], 1, H, dim,
-                                   vdim, None, True)
+            K.lightning_chunks(dev(x[r0:r1]), 0, 8, 16, dev(pw), state, *seg, *_chunk_lists([0, r1 - r0]), o[r0:r1], 1, H, dim, vdim,
+                               None, True)
     got = o.cpu().double().numpy().reshape(T, 1, 8)
     assert np.abs(want[-1]).max() > 50 * np.abs(want[2]).max()            # the far key dominates the end
-    # (the chunked kernel multiplies the state by a float32 power of the decay once a chunk: 47 roundings)
+    # (the chunked kernels multiply the state by a float32 power of the decay once a chunk: 47 roundings)
     assert np.abs(got - want).max() <= (2e-6 if kernel == "scan" else 1e-5) * np.abs(want).max()
 
 
