@@ -385,7 +385,7 @@ int kp_lightning_scan(const void* qkv, int ld, int q_col, int k_col, int v_col, 
 // Rows of a chunk of the chunked form (the decay table holds a^0 .. a^rows for every head).
 int kp_lightning_chunk_rows() { return LC_C; }
 
-// The chunked form: the contract of kp_lightning_scan with the decays given as powers, decay_pow [H][rows + 1] = a_h^m,
+// The chunked form: the arguments of kp_lightning_scan with the decays given as powers, decay_pow [H][rows + 1] = a_h^m,
 // and the list of chunks.  KP_ERR_UNSUPPORTED for heads it does not take (dim > 128).  chunk_seg, chunk_row0 [n_chunks]: every chunk's segment and first row
 // (chunks of at most kp_lightning_chunk_rows() rows, a segment's chunks in order and side by side); seg_chunk0 [n_seg + 1]:
 // the first chunk of every segment; scratch: n_chunks * H * dim * vdim floats.
