@@ -19,8 +19,9 @@ the same.
 This file is the only place that knows the design's ``config.json`` keys and tensor names.  The layers are listed
 in ``layers``, each with its ``type`` (the mixer), the mixer's sizes (``mixer``) and its feed-forward (``mlp``, or
 null for none); layer i's tensors start with ``l<i>.``.  Every size and constant is read from there; what the
-design fixes (activations, the kinds of gates, the place of the norms) is written below.  ``loop`` and
-``token_side`` may be left out: the model then has no loop, or no side inputs.
+design fixes (activations, the kinds of gates, the place of the norms) is written below.  ``loop``,
+``token_side``, ``embedding`` and ``logit_scale`` may be left out: the model then has no loop, no side inputs, an
+embedding that is not scaled, logits that are not scaled.
 """
 from __future__ import annotations
 
@@ -60,7 +61,7 @@ class VekuzenConfig(TypedConfig):
     width: int = cfg()
     layers: List[dict] = cfg()
     norm: dict = cfg()
-    embedding: dict = cfg()
+    embedding: Optional[dict] = cfg(None)
     max_positions: int = cfg()
     logit_scale: float = cfg(1.0)
     loop: Optional[dict] = cfg(None)
@@ -77,7 +78,8 @@ class VekuzenConfig(TypedConfig):
         self.eps = float(_get(self.norm, "eps", "norm"))
         if self.eps <= 0:
             raise ConfigError("norm.eps must be positive")
-        self.embedding_scale = float(_get(self.embedding, "scale", "embedding"))
+        # (an embedding without a scale is not scaled)
+        self.embedding_scale = float(_get(self.embedding, "scale", "embedding")) if self.embedding is not None else 1.0
         self.side_dim = _int(self.token_side, "dim", "token_side") if self.token_side is not None else None
         n = len(self.layers)
         if self.loop is not None:

@@ -72,7 +72,7 @@ def test_no_loop_and_no_side_inputs_mean_no_such_tensors():
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.pop("max_positions"), "max_positions"),
     (lambda c: c["token_side"].pop("dim"), "dim"),
-    (lambda c: c.pop("embedding"), "embedding"),
+    (lambda c: c["embedding"].pop("scale"), "scale"),
 ])
 def test_configuration_errors_name_the_key(change, word):
     from kappai_b200.config.schema import ConfigError
@@ -81,6 +81,15 @@ def test_configuration_errors_name_the_key(change, word):
     with pytest.raises(ConfigError) as e:
         _spec(cfg)
     assert word in str(e.value)
+
+
+def test_keys_that_may_be_left_out():
+    cfg = copy.deepcopy(CONFIGS["A"][0])
+    for k in ("embedding", "logit_scale", "loop", "token_side"):
+        cfg.pop(k)
+    spec = _spec(cfg)
+    assert spec.embedding.params["scale"] == 1.0 and spec.head.params["scale"] == 1.0
+    assert spec.entry is None and spec.token_table is None and [e.layer for e in spec.schedule] == [0, 1, 2]
 
 
 def test_missing_and_unexpected_tensors_are_listed(tmp_path):
