@@ -42,21 +42,26 @@ CHUNKED_FROM = 16      # rows of a step's longest segment from which the chunked
 def lightning_chunks(segs, chunk_rows: int):
     """The chunks of a step's segments for the chunked kernels (``engine.batch.StepSegments`` in,
     ``engine.batch.PartTables`` out; None for a step of short segments only, which the scan takes): every segment cut
-    into stretches of at most ``chunk_rows`` rows, counted from its first row in this step."""
+    into stretches of at most ``chunk_rows`` rows, counted from its first row in this step.  The short segments that
+    lead the step (decoded tokens, as the scheduler orders them) are left to the scan, which walks a one-row segment
+    in a fraction of a chunk's time: ``n_lead`` counts them, and the lists number the other segments from 0."""
     from ..engine.batch import PartTables
 
     if segs.max_seg_len < CHUNKED_FROM:
         return None
     cu = segs.cu_rows
+    n_lead = 0
+    while segs.seg_len[n_lead] < CHUNKED_FROM:
+        n_lead += 1
     chunk_seg, chunk_row0, seg_chunk0 = [], [], [0]
-    for i in range(segs.n_seg):
+    for i in range(n_lead, segs.n_seg):
         for r0 in range(int(cu[i]), int(cu[i + 1]), chunk_rows):
-            chunk_seg.append(i)
+            chunk_seg.append(i - n_lead)
             chunk_row0.append(r0)
         seg_chunk0.append(len(chunk_seg))
     i32 = lambda v: np.asarray(v, dtype=np.int32)
     return PartTables(arrays={"chunk_seg": i32(chunk_seg), "chunk_row0": i32(chunk_row0), "seg_chunk0": i32(seg_chunk0)},
-                      scalars={"n_chunks": len(chunk_seg)})
+                      scalars={"n_chunks": len(chunk_seg), "n_lead": n_lead})
 
 
 class LightningAttention(Part):
@@ -123,14 +128,18 @@ class LightningAttention(Part):
         p = linear(h, self.w_in)                                 # [q | k | v | gate]
         o = torch.empty((n, H * vdim), dtype=torch.float32, device=p.device)
         chunks = ctx.tables.get(self.step_tables_key) if self.chunked else None
+        scan = lambda n_seg: K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows,
+                                              ctx.seg_pos, ctx.seg_slot, o, n_seg, H, dim, vdim, self.activation, cache.writes)
         if chunks is not None:
             # (measured at 2,048 rows against the scan: 32 heads of 64 x 64 151 us against 430, of 128 x 128 620 against 1291)
-            K.lightning_chunks(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows, ctx.seg_pos, ctx.seg_slot,
-                               chunks.chunk_seg, chunks.chunk_row0, chunks.seg_chunk0, chunks.n_chunks, o, ctx.n_seg, H, dim,
-                               vdim, self.activation, cache.writes)
+            nl = chunks.n_lead
+            if nl:
+                scan(nl)                                         # decoded tokens beside the portions: the scan takes them
+            K.lightning_chunks(p, 0, H * dim, 2 * H * dim, self.decay_pow, cache.tensor, ctx.cu_rows[nl:], ctx.seg_pos[nl:],
+                               ctx.seg_slot[nl:], chunks.chunk_seg, chunks.chunk_row0, chunks.seg_chunk0, chunks.n_chunks, o,
+                               ctx.n_seg - nl, H, dim, vdim, self.activation, cache.writes)
         else:
-            K.lightning_scan(p, 0, H * dim, 2 * H * dim, self.decay_hi, self.decay_lo, cache.tensor, ctx.cu_rows, ctx.seg_pos,
-                             ctx.seg_slot, o, ctx.n_seg, H, dim, vdim, self.activation, cache.writes)
+            scan(ctx.n_seg)
         g0 = 2 * H * dim + H * vdim
         og = torch.empty((n, H * vdim), dtype=p.dtype, device=p.device)
         K.norm_gate_rows(o, self.norm_w, p[:, g0:g0 + H * vdim], self.eps, og)

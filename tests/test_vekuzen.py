@@ -177,3 +177,20 @@ def test_plain_model_prefix_property():
     toks = list(np.random.default_rng(1).integers(0, 19, 23))
     full = m.forward(toks)
     assert np.allclose(m.forward(toks[:11]), full[:11], atol=1e-9)
+
+
+def test_chunk_list_of_the_lightning_kernels():
+    """Segments in chunks of 64 rows from their first row in the step; the short segments that lead are left out
+    (the scan takes them) and the others are numbered from 0; a short segment further on keeps its chunk."""
+    from kappai_b200.engine.batch import StepSegments
+    from kappai_b200.parts.lightning import CHUNKED_FROM, lightning_chunks
+    lens = [1, 3, 100, 1, 70]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    t = lightning_chunks(StepSegments(sum(lens), 5, cu, np.zeros(5, np.int32), lens, max(lens), False), 64)
+    assert t.scalars == {"n_chunks": 5, "n_lead": 2}
+    assert t.arrays["chunk_seg"].tolist() == [0, 0, 1, 2, 2]
+    assert t.arrays["chunk_row0"].tolist() == [4, 68, 104, 105, 169]
+    assert t.arrays["seg_chunk0"].tolist() == [0, 2, 3, 5]
+    short = [CHUNKED_FROM - 1, 1]
+    cu = np.array([0, short[0], sum(short)], np.int32)
+    assert lightning_chunks(StepSegments(sum(short), 2, cu, np.zeros(2, np.int32), short, max(short), False), 64) is None
